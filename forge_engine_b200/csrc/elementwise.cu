@@ -1,0 +1,140 @@
+// Embedding gather, fused residual-add + RMSNorm, SiLU*mul.
+//
+// Upstream counterparts: nn.Embedding (src/forge_engine/qwen3.py:325), the fused
+// residual RMSNorm (src/forge_engine/_triton_kernels.py:32-58; plain form
+// src/forge_engine/kernels/__init__.py:12-26) and F.silu(gate) * up
+// (src/forge_engine/qwen3.py:227).  The residual stream is kept in 32-bit.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// embedding: residual[n, :] = float(table[ids[n], :])
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  float* dst = out + (size_t)row * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, FE_STATUS_BAD_TOKEN);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  const T* src = table + (size_t)id * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+FE_EXPORT int fe_embedding(const int* ids, const void* table, int table_dtype, float* out,
+                           int n, int hidden, int vocab, int* status, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == FE_DTYPE_F32)
+    embedding_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, status);
+  else if (table_dtype == FE_DTYPE_BF16)
+    embedding_kernel<bf16><<<n, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, status);
+  else
+    return FE_ERR_BAD_DTYPE;
+  return fe_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// x = residual[src] + update[src];  residual[src] = x (optional);
+// out[r] = x * rsqrt(mean(x^2) + eps) * weight       -- all in 32-bit, one rounding
+// src = row_map ? row_map[r] : r
+// ---------------------------------------------------------------------------
+template <typename TU, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ update,
+                                   const float* __restrict__ weight, TO* __restrict__ out,
+                                   const int* __restrict__ row_map, int size, float eps,
+                                   int write_residual) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = row_map ? row_map[r] : r;
+  float* res = residual + (size_t)src * size;
+  const TU* upd = update ? update + (size_t)src * size : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < size; i += blockDim.x) {
+    float x = res[i];
+    if (upd) x += to_float(upd[i]);
+    if (write_residual) res[i] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)size + eps);
+  TO* dst = out + (size_t)r * size;
+  for (int i = threadIdx.x; i < size; i += blockDim.x) {
+    float x = res[i];
+    if (upd && !write_residual) x += to_float(upd[i]);
+    dst[i] = from_float<TO>(x * inv * weight[i]);
+  }
+}
+
+FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dtype,
+                             const float* weight, void* out, int out_dtype, const int* row_map,
+                             int rows, int size, float eps, int write_residual,
+                             cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  int threads = 32;
+  while (threads < 512 && threads * 4 < size) threads <<= 1;
+#define LAUNCH(TU, TO)                                                                  \
+  add_rmsnorm_kernel<TU, TO><<<rows, threads, 0, stream>>>(residual, (const TU*)update, \
+      weight, (TO*)out, row_map, size, eps, write_residual)
+  if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH(float, float);
+  else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH(bf16, bf16);
+  else if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) LAUNCH(float, bf16);
+  else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_F32) LAUNCH(bf16, float);
+  else return FE_ERR_BAD_DTYPE;
+#undef LAUNCH
+  return fe_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// out[n, i] = silu(gate_up[n, i]) * gate_up[n, inter + i]
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  const int row = blockIdx.x;
+  const T* g = gate_up + (size_t)row * 2 * inter;
+  const T* u = g + inter;
+  T* o = out + (size_t)row * inter;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i < inter) o[i] = from_float<T>(silu(to_float(g[i])) * to_float(u[i]));
+}
+
+template <typename T>
+__global__ void silu_mul_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  const int row = blockIdx.x;
+  const T* g = gate_up + (size_t)row * 2 * inter;
+  const T* u = g + inter;
+  T* o = out + (size_t)row * inter;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= inter) return;
+  float a[8], b[8];
+  load8(g + i, a);
+  load8(u + i, b);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a[k] = silu(a[k]) * b[k];
+  store8(o + i, a);
+}
+
+FE_EXPORT int fe_silu_mul(const void* gate_up, void* out, int dtype, int rows, int inter,
+                          cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const bool vec = (inter % 8) == 0 && ((uintptr_t)gate_up % 32) == 0 && ((uintptr_t)out % 32) == 0;
+  const int threads = 256;
+  const int per = vec ? 8 : 1;
+  dim3 grid(rows, (inter + threads * per - 1) / (threads * per));
+  if (grid.y > 65535) return FE_ERR_TOO_LARGE;
+  if (dtype == FE_DTYPE_F32) {
+    if (vec) silu_mul_vec8_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+    else silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+  } else if (dtype == FE_DTYPE_BF16) {
+    if (vec) silu_mul_vec8_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
+    else silu_mul_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
+  } else {
+    return FE_ERR_BAD_DTYPE;
+  }
+  return fe_last_error();
+}

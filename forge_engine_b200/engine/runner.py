@@ -1,0 +1,159 @@
+"""The step function: model + cache manager + one call that runs a mixed batch.
+
+``ModelRunner.step(entries)`` is the only way tokens reach the model.  The scheduler,
+the Python entry point, the command line and the trace-replay tool all call it.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import read_model_config
+from ..errors import ForgeEngineError, KVCacheCapacityError
+from ..models.decoder import DecoderModel, expected_tensors
+from ..ops import native
+from ..parts.base import BuildContext
+from ..weights.loader import load_checkpoint
+from ..weights.random_init import random_tensors
+from .batch import StepBatch, StepEntry, build_batch
+
+DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16,
+          "fp32": torch.float32}
+
+
+def resolve_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError("dtype must be bfloat16 or float32")
+        return name
+    try:
+        return DTYPES[name]
+    except KeyError:
+        raise ValueError(f"dtype {name!r} must be 'bfloat16' or 'float32'") from None
+
+
+class ModelRunner:
+    """Owns the model, the cache manager and the device status word."""
+
+    def __init__(self, model: DecoderModel, *, page_size: int, num_pages: int, max_requests: int) -> None:
+        self.model = model
+        self.ctx = model.ctx
+        needs, shares = model.cache_needs()
+        self.cache = CacheManager(
+            needs,
+            page_size=page_size,
+            num_pages=num_pages,
+            max_requests=max_requests,
+            dtype=self.ctx.dtype,
+            device=self.ctx.device,
+            shares=shares,
+        )
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # -- construction ------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder: str | Path, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+                    num_pages: int = 1024, max_requests: int = 16) -> "ModelRunner":
+        """Model class by config.json's architecture, weights by tensor name."""
+        native.require_cuda()
+        native.lib()
+        engine_dtype = resolve_dtype(dtype)
+        _, _, spec = read_model_config(folder)
+        expected = expected_tensors(spec)
+        optional = (spec.head_name,) if spec.tie_embeddings else ()
+        weights = load_checkpoint(folder, expected, engine_dtype, device, optional)
+        return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
+                                num_pages=num_pages, max_requests=max_requests)
+
+    @classmethod
+    def from_random(cls, config: dict, seed: int, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+                    num_pages: int = 1024, max_requests: int = 16, std: float = 0.02) -> "ModelRunner":
+        """Random weights drawn on the device (benchmark-sized models never touch the disk)."""
+        native.require_cuda()
+        native.lib()
+        engine_dtype = resolve_dtype(dtype)
+        _, _, spec = read_model_config(config)
+        weights = random_tensors(expected_tensors(spec), seed, std=std, dtype=engine_dtype, device=device)
+        return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
+                                num_pages=num_pages, max_requests=max_requests)
+
+    @classmethod
+    def from_tensors(cls, spec, weights: dict, *, dtype, device, page_size: int, num_pages: int,
+                     max_requests: int) -> "ModelRunner":
+        native.require_cuda()
+        native.lib()
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        ctx = BuildContext(dtype=resolve_dtype(dtype), device=torch.device(device), status=status)
+        with torch.cuda.device(ctx.device):
+            model = DecoderModel(spec, weights, ctx)
+            return cls(model, page_size=page_size, num_pages=num_pages, max_requests=max_requests)
+
+    # -- requests ------------------------------------------------------------------------
+    def begin(self, key) -> None:
+        self.cache.begin_request(key)
+
+    def end(self, key) -> None:
+        self.cache.end_request(key)
+
+    # -- the step ------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens as one batch from the cache earlier steps left.
+
+        Returns 32-bit logits [number of wanted places, vocab] on the device, ordered by
+        entry and by ``want``.  Pages are leased before anything runs; if they run out,
+        nothing has changed and KVCacheCapacityError is raised."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        keys = [e.key for e in entries]
+        if len(set(keys)) != len(keys):
+            raise ValueError("a request may appear only once in a step")
+        vocab = self.model.spec.vocab_size
+        for entry in entries:
+            if len(entry.tokens) < 1:
+                raise ValueError(f"request {entry.key!r} brings no tokens")
+            for token in entry.tokens:
+                if not 0 <= int(token) < vocab:
+                    raise ValueError(f"request {entry.key!r}: token id {token} is outside the vocabulary")
+            request = self.cache.request(entry.key)
+            if request.length + len(entry.tokens) > self.model.spec.max_positions:
+                raise ForgeEngineError(
+                    f"request {entry.key!r} would exceed max_position_embeddings="
+                    f"{self.model.spec.max_positions}"
+                )
+        reserved = []
+        try:
+            for entry in entries:
+                request = self.cache.request(entry.key)
+                self.cache.reserve(entry.key, request.length + len(entry.tokens))
+                reserved.append(entry.key)
+        except KVCacheCapacityError:
+            for key in reserved:
+                self.cache.trim(key, self.cache.request(key).length)
+            raise
+        try:
+            with torch.cuda.device(self.ctx.device):
+                batch = build_batch(entries, self.cache, self.ctx.device)
+                logits = self.model.forward(batch, self.cache)
+        except BaseException:
+            for key in reserved:
+                self.cache.trim(key, self.cache.request(key).length)
+            raise
+        for entry in entries:
+            request = self.cache.request(entry.key)
+            self.cache.advance(entry.key, request.length + len(entry.tokens))
+        self.steps_run += 1
+        self.tokens_run += batch.n_tokens
+        return logits
+
+    def check_status(self) -> None:
+        """Read the device status word (synchronises) and raise if a kernel flagged anything."""
+        value = int(self.ctx.status.item())
+        if value:
+            self.ctx.status.zero_()
+            reasons = [text for bit, text in native.STATUS_BITS.items() if value & bit]
+            raise ForgeEngineError("device status: " + "; ".join(reasons))

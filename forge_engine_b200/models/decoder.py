@@ -1,0 +1,108 @@
+"""A decoder-only language model assembled from a ModelSpec.
+
+Data flow of one step (src/forge_engine/qwen3.py:297-342, restated for a flat batch):
+embedding gather into the 32-bit residual stream, the runs of the schedule in order
+(each a block with its cache view), final norm on the wanted rows only, and the output
+projection to 32-bit logits.  Which blocks exist, which run uses which block and which
+cache, is all data of the spec; this class has no sizes of its own.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import ModelSpec
+from ..ops import native
+from ..parts.base import BuildContext, WeightInfo, arrangement_class, build_part, part_class
+from ..parts.linear import Linear
+
+
+def expected_tensors(spec: ModelSpec) -> dict:
+    """Checkpoint tensor name -> WeightInfo, in a fixed order (embedding, final norm,
+    layers in order, output head), as upstream lists them (src/forge_engine/weights.py:253-282)."""
+    out: dict[str, WeightInfo] = {
+        spec.embed_name: WeightInfo((spec.vocab_size, spec.hidden_size)),
+    }
+    for local, info in part_class(spec.final_norm).weight_shapes(spec.final_norm).items():
+        out[f"{spec.final_norm_name}.{local}"] = info
+    for layer in spec.layers:
+        block = arrangement_class(layer.arrangement)
+        for role, shapes in block.weight_shapes(layer).items():
+            prefix = layer.names[role]
+            for local, info in shapes.items():
+                out[f"{prefix}.{local}"] = info
+    if not spec.tie_embeddings:
+        out[spec.head_name] = WeightInfo((spec.vocab_size, spec.hidden_size))
+    return out
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, weights: dict, ctx: BuildContext) -> None:
+        self.spec = spec
+        self.ctx = ctx
+        self.embed = weights[spec.embed_name].contiguous()
+        self.blocks = []
+        for layer in spec.layers:
+            block_cls = arrangement_class(layer.arrangement)
+            per_role = {}
+            for role, shapes in block_cls.weight_shapes(layer).items():
+                prefix = layer.names[role]
+                per_role[role] = {local: weights[f"{prefix}.{local}"] for local in shapes}
+            self.blocks.append(block_cls(layer, per_role, ctx))
+        norm_shapes = part_class(spec.final_norm).weight_shapes(spec.final_norm)
+        self.final_norm = build_part(
+            spec.final_norm,
+            {local: weights[f"{spec.final_norm_name}.{local}"] for local in norm_shapes},
+            ctx,
+        )
+        self.head = Linear(self.embed if spec.tie_embeddings else weights[spec.head_name])
+        for index, run in enumerate(spec.schedule):
+            if not 0 <= run.layer < len(self.blocks):
+                raise ValueError(f"run {index} names layer {run.layer}, which does not exist")
+            if run.cache_of is not None and not 0 <= run.cache_of < index:
+                raise ValueError(f"run {index} may only read the cache of an earlier run")
+
+    # -- cache ---------------------------------------------------------------------
+    def cache_needs(self) -> tuple:
+        """(needs per run, {run: run whose cache it reads})."""
+        needs = [self.blocks[run.layer].cache_needs() for run in self.spec.schedule]
+        shares = {i: run.cache_of for i, run in enumerate(self.spec.schedule) if run.cache_of is not None}
+        return needs, shares
+
+    def weight_bytes(self) -> int:
+        """Bytes of every distinct weight tensor a step reads once."""
+        seen, total = set(), 0
+
+        def visit(obj) -> None:
+            nonlocal total
+            if isinstance(obj, torch.Tensor):
+                if obj.data_ptr() not in seen:
+                    seen.add(obj.data_ptr())
+                    total += obj.numel() * obj.element_size()
+            elif isinstance(obj, Linear):
+                visit(obj.weight)
+            elif hasattr(obj, "__dict__"):
+                for value in vars(obj).values():
+                    if isinstance(value, (torch.Tensor, Linear)) or hasattr(value, "__dict__"):
+                        if not isinstance(value, (BuildContext, type)) and value is not self.spec:
+                            visit(value)
+
+        for block in self.blocks:
+            visit(block)
+        visit(self.final_norm)
+        visit(self.head)
+        return total
+
+    # -- one step ------------------------------------------------------------------
+    def forward(self, batch, cache) -> torch.Tensor:
+        """Run ``batch`` through all runs; returns logits [wanted rows, vocab] in 32-bit."""
+        n = batch.n_tokens
+        h = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.ctx.device)
+        native.embedding(batch.token_ids, self.embed, h, self.ctx.status)
+        pending = None
+        for index, run in enumerate(self.spec.schedule):
+            pending = self.blocks[run.layer].forward(h, pending, batch, cache.view(index))
+        if batch.n_want == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.ctx.device)
+        normed = self.final_norm.add_forward(h, pending, row_map=batch.want_rows)
+        return self.head(normed, out_dtype=torch.float32)

@@ -1,0 +1,280 @@
+"""ctypes binding of the kernel library and thin tensor-level wrappers.
+
+Every wrapper checks dtype, device and contiguity, passes raw pointers and the
+current CUDA stream, and raises on a non-zero return.  There is no fallback: without
+a CUDA device or without the library these functions raise ``CUDAUnavailableError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_ulonglong, c_void_p
+
+import torch
+
+from ..errors import CUDAUnavailableError, ForgeEngineError, UnsupportedShapeError
+from .build import library_path
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_BITS = {
+    1: "a token id lies outside the vocabulary",
+    2: "a block-table entry is negative or outside the page pool",
+    4: "a position lies outside its request's block table",
+    8: "a bounded wait inside a kernel ran out",
+    16: "logits contain NaN or +inf",
+}
+
+_ERRORS = {
+    10001: "unsupported dtype combination",
+    10002: "unsupported shape",
+    10003: "pointer or stride not aligned as the kernel needs",
+    10004: "size beyond what the kernel can launch",
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load (building first if needed) the kernel library exactly once."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        try:
+            _lib = ctypes.CDLL(str(path))
+        except OSError as error:
+            raise CUDAUnavailableError(f"cannot load {path}: {error}") from error
+        _declare(_lib)
+    return _lib
+
+
+def _declare(handle: ctypes.CDLL) -> None:
+    p, i, f = c_void_p, c_int, c_float
+    signatures = {
+        "fe_embedding": [p, p, i, p, i, i, i, p, p],
+        "fe_add_rmsnorm": [p, p, i, p, p, i, p, i, i, f, i, p],
+        "fe_silu_mul": [p, p, i, i, i, p],
+        "fe_qk_rope_cache": [p, i, p, p, f, p, i, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
+        "fe_attention_simt": [p, i, i, p, p, p, i, i, i, p, p, i, f, p, i, i, i, i, p, p],
+        "fe_gemm_simt": [p, i, p, i, p, p, i, i, i, i, i, p],
+        "fe_sample": [p, i, i, p, p, p, p, p, p, p, p, p],
+    }
+    for name, argtypes in signatures.items():
+        fn = getattr(handle, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    handle.fe_uniform_host.argtypes = [c_ulonglong, c_ulonglong]
+    handle.fe_uniform_host.restype = c_float
+
+
+def has_symbol(name: str) -> bool:
+    return hasattr(lib(), name)
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code in _ERRORS:
+        raise UnsupportedShapeError(f"{what}: {_ERRORS[code]}")
+    raise ForgeEngineError(f"{what}: CUDA error {code}")
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise CUDAUnavailableError("no CUDA device: this engine runs on the GPU only")
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise UnsupportedShapeError(f"dtype {t.dtype} is neither float32 nor bfloat16") from None
+
+
+def _dense(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise CUDAUnavailableError(f"{name} must live on the CUDA device")
+    if not t.is_contiguous():
+        raise UnsupportedShapeError(f"{name} must be contiguous")
+    return t
+
+
+# ---------------------------------------------------------------------------
+# wrappers
+# ---------------------------------------------------------------------------
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[n] = float(table[ids[n]]); out is the 32-bit residual stream [N, H]."""
+    _dense(ids, "ids"), _dense(table, "table"), _dense(out, "out")
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32
+    n, hidden = out.shape
+    check(
+        lib().fe_embedding(ptr(ids), ptr(table), code(table), ptr(out), n, hidden, table.shape[0],
+                           ptr(status), stream()),
+        "embedding",
+    )
+
+
+def add_rmsnorm(
+    residual: torch.Tensor,
+    update: torch.Tensor | None,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    eps: float,
+    row_map: torch.Tensor | None = None,
+    write_residual: bool = True,
+) -> None:
+    """residual += update (32-bit, in place unless ``write_residual`` is false);
+    out = rmsnorm(residual) * weight.  With ``row_map`` row r of ``out`` comes from
+    row ``row_map[r]`` of ``residual`` and ``update``."""
+    _dense(residual, "residual"), _dense(weight, "weight"), _dense(out, "out")
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32
+    rows, size = out.shape
+    assert residual.shape[1] == size and weight.numel() == size
+    if update is not None:
+        _dense(update, "update")
+        assert update.shape == residual.shape
+    if row_map is not None:
+        assert row_map.dtype == torch.int32 and row_map.numel() == rows
+    else:
+        assert residual.shape[0] == rows
+    check(
+        lib().fe_add_rmsnorm(
+            ptr(residual), ptr(update), code(update) if update is not None else code(out),
+            ptr(weight), ptr(out), code(out), ptr(row_map), rows, size, float(eps),
+            1 if write_residual else 0, stream(),
+        ),
+        "add_rmsnorm",
+    )
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]."""
+    _dense(gate_up, "gate_up"), _dense(out, "out")
+    rows, inter = out.shape
+    assert gate_up.shape == (rows, 2 * inter) and gate_up.dtype == out.dtype
+    check(lib().fe_silu_mul(ptr(gate_up), ptr(out), code(out), rows, inter, stream()), "silu_mul")
+
+
+def qk_rope_cache(
+    qkv: torch.Tensor,
+    q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None,
+    eps: float,
+    inv_freq: torch.Tensor | None,
+    rotary_dim: int,
+    positions: torch.Tensor,
+    token_entry: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    num_q_heads: int,
+    write_kv: bool,
+    status: torch.Tensor,
+) -> None:
+    """Normalise and rotate q (in place) and k, and store k, v into their pages.
+
+    qkv is [N, (nq + 2 nkv) * D]; the caches are [pages, nkv, page_size, D]."""
+    _dense(qkv, "qkv"), _dense(k_cache, "k_cache"), _dense(v_cache, "v_cache")
+    _dense(block_table, "block_table")
+    num_pages, nkv, page_size, head_dim = k_cache.shape
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (num_q_heads + 2 * nkv) * head_dim
+    assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2
+    assert positions.dtype == torch.int32 and token_entry.dtype == torch.int32
+    for w in (q_weight, k_weight, inv_freq):
+        assert w is None or (w.dtype == torch.float32 and w.is_cuda and w.is_contiguous())
+    check(
+        lib().fe_qk_rope_cache(
+            ptr(qkv), code(qkv), ptr(q_weight), ptr(k_weight), float(eps), ptr(inv_freq),
+            int(rotary_dim), ptr(positions), ptr(token_entry), ptr(k_cache), ptr(v_cache),
+            ptr(block_table), block_table.shape[1], page_size, num_pages, num_q_heads, nkv,
+            head_dim, n, 1 if write_kv else 0, ptr(status), stream(),
+        ),
+        "qk_rope_cache",
+    )
+
+
+def attention_simt(
+    q: torch.Tensor,
+    q_stride: int,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    positions: torch.Tensor,
+    token_entry: torch.Tensor,
+    window: int | None,
+    scale: float,
+    out: torch.Tensor,
+    num_q_heads: int,
+    status: torch.Tensor,
+) -> None:
+    """General paged causal attention; q row n starts at q + n * q_stride elements."""
+    num_pages, nkv, page_size, head_dim = k_cache.shape
+    n = out.shape[0]
+    assert out.shape[1] == num_q_heads * head_dim and out.dtype == q.dtype == k_cache.dtype
+    check(
+        lib().fe_attention_simt(
+            ptr(q), int(q_stride), code(q), ptr(k_cache), ptr(v_cache), ptr(block_table),
+            block_table.shape[1], page_size, num_pages, ptr(positions), ptr(token_entry),
+            int(window or 0), float(scale), ptr(out), num_q_heads, nkv, head_dim, n, ptr(status),
+            stream(),
+        ),
+        "attention_simt",
+    )
+
+
+def gemm_simt(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    out: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    accumulate: bool = False,
+) -> None:
+    """out = x @ w.T (+ bias) (+ out) with plain 32-bit FMAs; w is [out, in]."""
+    _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
+    n, k = x.shape
+    o = w.shape[0]
+    assert w.shape[1] == k and out.shape == (n, o)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == o)
+    check(
+        lib().fe_gemm_simt(ptr(x), code(x), ptr(w), code(w), ptr(bias), ptr(out), code(out), n, o, k,
+                           1 if accumulate else 0, stream()),
+        "gemm_simt",
+    )
+
+
+def sample(
+    logits: torch.Tensor,
+    out: torch.Tensor,
+    status: torch.Tensor,
+    temperature: torch.Tensor | None = None,
+    top_k: torch.Tensor | None = None,
+    top_p: torch.Tensor | None = None,
+    min_p: torch.Tensor | None = None,
+    seeds: torch.Tensor | None = None,
+    counters: torch.Tensor | None = None,
+) -> None:
+    """One token per row of 32-bit logits; all parameter tensors are per row."""
+    _dense(logits, "logits")
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() >= rows
+    for t, dt in ((temperature, torch.float32), (top_k, torch.int32), (top_p, torch.float32),
+                  (min_p, torch.float32), (seeds, torch.int64), (counters, torch.int64)):
+        assert t is None or (t.dtype == dt and t.is_cuda and t.numel() >= rows)
+    check(
+        lib().fe_sample(ptr(logits), rows, vocab, ptr(temperature), ptr(top_k), ptr(top_p), ptr(min_p),
+                        ptr(seeds), ptr(counters), ptr(out), ptr(status), stream()),
+        "sample",
+    )

@@ -1,0 +1,91 @@
+"""Causal grouped-query attention over the paged cache.
+
+Formulas: src/forge_engine/qwen3.py:108-207.  One fused projection gives q, k, v; one
+kernel normalises q and k per head, rotates them and stores k, v into their pages; the
+attention kernel then reads everything it needs from the pages, so a step's new tokens
+and the earlier ones are treated alike.  The mixer keeps PagedKVSpec(kv heads,
+head_dim, window) between steps.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import CacheNeeds, PagedKVSpec
+from ..errors import UnsupportedShapeError
+from ..ops import native
+from .base import BuildContext, CacheView, Mixer, WeightInfo, build_part, register_part
+from .linear import Linear, fuse_rows
+
+
+class GQAttention(Mixer):
+    def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
+        if spec.head_dim % 16 or spec.head_dim > 256:
+            raise UnsupportedShapeError(
+                f"head_dim={spec.head_dim}: the attention kernels take multiples of 16 up to 256"
+            )
+        if spec.num_heads % spec.num_kv_heads:
+            raise UnsupportedShapeError("num_heads must be a multiple of num_kv_heads")
+        self.spec = spec
+        self.ctx = ctx
+        self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        bias = None
+        if spec.bias:
+            bias = fuse_rows([weights["q_proj.bias"], weights["k_proj.bias"], weights["v_proj.bias"]])
+        self.qkv_proj = Linear(
+            fuse_rows([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]]),
+            bias,
+        )
+        self.o_proj = Linear(weights["o_proj.weight"], weights.get("o_proj.bias") if spec.bias else None)
+        self.q_norm = self.k_norm = None
+        if spec.qk_norm:
+            self.q_norm = weights["q_norm.weight"].float().contiguous()
+            self.k_norm = weights["k_norm.weight"].float().contiguous()
+        self.position = build_part(spec.position, {}, ctx)
+
+    @classmethod
+    def weight_shapes(cls, spec) -> dict:
+        q, kv, h = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.hidden_size
+        shapes = {
+            "q_proj.weight": WeightInfo((q, h)),
+            "k_proj.weight": WeightInfo((kv, h)),
+            "v_proj.weight": WeightInfo((kv, h)),
+            "o_proj.weight": WeightInfo((h, q)),
+        }
+        if spec.qk_norm:
+            shapes["q_norm.weight"] = WeightInfo((spec.head_dim,), "norm")
+            shapes["k_norm.weight"] = WeightInfo((spec.head_dim,), "norm")
+        if spec.bias:
+            shapes["q_proj.bias"] = WeightInfo((q,), "bias")
+            shapes["k_proj.bias"] = WeightInfo((kv,), "bias")
+            shapes["v_proj.bias"] = WeightInfo((kv,), "bias")
+            shapes["o_proj.bias"] = WeightInfo((h,), "bias")
+        return shapes
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(kv=PagedKVSpec(self.nkv, self.d, self.spec.window))
+
+    def forward(self, x, batch, cache: CacheView):
+        qkv = self.qkv_proj(x)
+        k_cache, v_cache = cache.kv
+        table = batch.group_tables[cache.group]
+        rotary = self.position.rotary()
+        if rotary is None:
+            self.position.apply(qkv, self.nq, self.nkv, self.d, batch)
+            inv_freq, rotary_dim = None, 0
+        else:
+            inv_freq, rotary_dim = rotary
+        native.qk_rope_cache(
+            qkv, self.q_norm, self.k_norm, self.spec.qk_norm_eps, inv_freq, rotary_dim,
+            batch.positions, batch.token_entry, k_cache, v_cache, table, self.nq,
+            cache.owns, self.ctx.status,
+        )
+        out = torch.empty((x.shape[0], self.nq * self.d), dtype=qkv.dtype, device=x.device)
+        native.attention_simt(
+            qkv, qkv.shape[1], k_cache, v_cache, table, batch.positions, batch.token_entry,
+            self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
+        )
+        return self.o_proj(out)
+
+
+register_part("gqa_attention", GQAttention, replace=True)

@@ -310,6 +310,7 @@ TINY_C = dict(
     attention_bias=True,
     rope_theta=50000.0,
     rms_norm_eps=3e-6,
+    eos_token_id=[329, 330],
 )
 
 
