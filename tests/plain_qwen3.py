@@ -39,6 +39,8 @@ class PlainConfig:
     rope_theta: float
     tie_word_embeddings: bool
     attention_bias: bool = False
+    sliding_window: int | None = None
+    max_window_layers: int = 0
 
     @classmethod
     def from_dict(cls, raw: dict) -> "PlainConfig":
@@ -56,7 +58,22 @@ class PlainConfig:
             rope_theta=float(raw["rope_theta"]),
             tie_word_embeddings=bool(raw.get("tie_word_embeddings", False)),
             attention_bias=bool(raw.get("attention_bias", False)),
+            sliding_window=(
+                int(raw["sliding_window"])
+                if raw.get("sliding_window") is not None
+                and raw.get("use_sliding_window", True)
+                else None
+            ),
+            max_window_layers=int(raw.get("max_window_layers", 0)),
         )
+
+    def window_of_layer(self, index: int) -> int | None:
+        """Upstream refuses any window (src/forge_engine/qwen3.py:44-45); with
+        ``use_sliding_window`` the layers from ``max_window_layers`` on see only the
+        last ``sliding_window`` keys (their own included).  This rests on the formula."""
+        if self.sliding_window is None or index < self.max_window_layers:
+            return None
+        return self.sliding_window
 
 
 def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
@@ -97,16 +114,23 @@ def apply_rotary(x: Tensor, cosine: Tensor, sine: Tensor) -> Tensor:
     return x * cosine.unsqueeze(0) + rotate_half(x) * sine.unsqueeze(0)
 
 
-def causal_mask(length: int, dtype: torch.dtype) -> Tensor:
-    """src/forge_engine/qwen3.py:384-406 with no past: key j is seen by query i iff j <= i."""
+def causal_mask(length: int, dtype: torch.dtype, window: int | None = None) -> Tensor:
+    """src/forge_engine/qwen3.py:384-406 with no past: key j is seen by query i iff j <= i
+    (and, with a window, i - j < window)."""
     positions = torch.arange(length)
     allowed = positions.unsqueeze(0) <= positions.unsqueeze(1)
+    if window is not None:
+        allowed = allowed & (positions.unsqueeze(1) - positions.unsqueeze(0) < window)
     mask = torch.zeros((length, length), dtype=dtype)
     return mask.masked_fill(~allowed, torch.finfo(dtype).min)
 
 
 def attention(
-    x: Tensor, weights: dict[str, Tensor], prefix: str, cfg: PlainConfig
+    x: Tensor,
+    weights: dict[str, Tensor],
+    prefix: str,
+    cfg: PlainConfig,
+    window: int | None = None,
 ) -> Tensor:
     """Causal grouped-query attention of one layer over a whole sequence.
 
@@ -134,7 +158,7 @@ def attention(
     k = k.repeat_interleave(groups, dim=0)
     v = v.repeat_interleave(groups, dim=0)
     scores = torch.matmul(q, k.transpose(1, 2)) * d**-0.5
-    scores = scores + causal_mask(length, scores.dtype)
+    scores = scores + causal_mask(length, scores.dtype, window)
     probabilities = torch.softmax(scores, dim=-1, dtype=torch.float32).to(q.dtype)
     out = torch.matmul(probabilities, v).transpose(0, 1).reshape(length, nq * d)
     return linear(out, weights[f"{prefix}.o_proj.weight"], bias("o_proj"))
@@ -153,7 +177,9 @@ def decoder_layer(
     """src/forge_engine/qwen3.py:241-261 - pre-norm block with two residual sums."""
     prefix = f"model.layers.{index}"
     normed = rms_norm(h, weights[f"{prefix}.input_layernorm.weight"], cfg.rms_norm_eps)
-    h = h + attention(normed, weights, f"{prefix}.self_attn", cfg)
+    h = h + attention(
+        normed, weights, f"{prefix}.self_attn", cfg, cfg.window_of_layer(index)
+    )
     # src/forge_engine/kernels/__init__.py:12-26: sum, then the same RMSNorm.
     normed = rms_norm(
         h, weights[f"{prefix}.post_attention_layernorm.weight"], cfg.rms_norm_eps
@@ -311,6 +337,26 @@ TINY_C = dict(
     rope_theta=50000.0,
     rms_norm_eps=3e-6,
     eos_token_id=[329, 330],
+)
+
+
+# Three layers, the last two windowed; nothing is a power of two.
+TINY_D = dict(
+    TINY_A,
+    vocab_size=203,
+    hidden_size=72,
+    intermediate_size=88,
+    num_hidden_layers=3,
+    num_attention_heads=6,
+    num_key_value_heads=2,
+    head_dim=16,
+    rms_norm_eps=2e-6,
+    rope_theta=20000.0,
+    tie_word_embeddings=False,
+    use_sliding_window=True,
+    sliding_window=11,
+    max_window_layers=1,
+    eos_token_id=202,
 )
 
 
