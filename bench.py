@@ -1,0 +1,311 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at the Qwen3-4B shape, one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with
+2,048-token contexts (device time of K decode steps through the step function);
+``e2e`` is the same through the Python entry point (``Engine.step``: host token ids in,
+sampled ids out, every step); ``prefill`` is one 2,048-token prompt in one step;
+``points`` holds decode at batch 1 and 64; ``roofline`` relates the decode step to the
+bytes it has to read.  Weights are random (seeded), token ids synthetic (seed 5).
+The contexts of the device-timed decode are cache pages filled with random numbers: a
+decode step's work does not depend on what the cached keys are.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIG_4B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "hidden_act": "silu",
+    "vocab_size": 151936,
+    "hidden_size": 2560,
+    "intermediate_size": 9728,
+    "num_hidden_layers": 36,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 128,
+    "max_position_embeddings": 8192,
+    "rms_norm_eps": 1e-6,
+    "rope_theta": 5000000.0,
+    "tie_word_embeddings": True,
+    "attention_bias": False,
+    "sliding_window": None,
+    "eos_token_id": None,
+}
+CONTEXT = 2048
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return float(raw["hbm_gbs"]), float(raw["bf16_tflops"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return FALLBACK_PEAKS["hbm_gbs"], FALLBACK_PEAKS["bf16_tflops"], "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self) -> None:
+        self.proc = None
+        self.lines: list = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(self.NAMES, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def reference_arm() -> int:
+    """The upstream project's public API loads one pinned Hugging Face checkpoint by
+    download; there is no network and no local copy, and it has no random-weights mode."""
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "upstream serves only the pinned Hub checkpoint Qwen/Qwen3-4B-Instruct-2507 "
+                       "(src/forge_engine/weights.py:55-70 downloads it); no network, no local snapshot, "
+                       "and its loader rejects any other config or random weights",
+    }))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--skip-points", action="store_true", help="skip batch 1/64, prefill and e2e")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
+        return 2
+    args.warmup = max(3, args.warmup)
+
+    import torch
+
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine, ModelRunner, StepEntry
+    from forge_engine_b200.ops import native
+
+    raw = dict(CONFIG_4B)
+    layers_full = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    layers = raw["num_hidden_layers"]
+    hbm_gbs, bf16_tflops, peak_source = peaks()
+    device = "cuda:0"
+    torch.cuda.set_device(0)
+    gen = torch.Generator().manual_seed(5)
+
+    max_batch = 64 if not args.skip_points else args.batch
+    steps_total = args.warmup + args.steps + 8
+    pages_per_request = -(-(CONTEXT + steps_total) // PAGE) + 1
+    num_pages = max_batch * pages_per_request + 8
+    runner = ModelRunner.from_random(raw, 0, dtype="bfloat16", device=device, page_size=PAGE,
+                                     num_pages=num_pages, max_requests=max_batch)
+    for group in runner.cache.groups:        # contexts: pages of random numbers
+        group.storage.normal_(0.0, 1.0)
+    weight_bytes = runner.model.weight_bytes()
+    kv_bytes_per_token = runner.cache.bytes_per_token()
+
+    def decode_run(batch: int, steps: int, warmup: int) -> tuple:
+        keys = [f"d{batch}-{i}" for i in range(batch)]
+        for key in keys:
+            runner.begin(key)
+            runner.cache.reserve(key, CONTEXT)
+            runner.cache.advance(key, CONTEXT)
+        tokens = torch.randint(0, raw["vocab_size"], (batch,), generator=gen).tolist()
+
+        def one_step():
+            return runner.step([StepEntry(k, [t], [0]) for k, t in zip(keys, tokens)])
+
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        launches_before = native.LAUNCHES
+        sampler = ClockSampler()
+        sampler.start()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(steps):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        clocks = sampler.stop()
+        launches = native.LAUNCHES - launches_before
+        runner.check_status()
+        for key in keys:
+            runner.end(key)
+        return ms, clocks, launches
+
+    ms_step, clocks, launches = decode_run(args.batch, args.steps, args.warmup)
+    value = args.batch / (ms_step / 1e3)
+    step_bytes = weight_bytes + args.batch * (CONTEXT + args.warmup + args.steps / 2) * kv_bytes_per_token
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    record = {
+        "metric": "decode tok/s (Qwen3-4B shape, bf16, batch 8, 2048-token contexts)",
+        "value": round(value, 2),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic token ids (seed 5), random weights (seed 0), contexts are random cache pages",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-4B shape",
+            "layers": layers,
+            "layers_full": layers_full,
+            "hidden": raw["hidden_size"],
+            "q_heads": raw["num_attention_heads"],
+            "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"],
+            "intermediate": raw["intermediate_size"],
+            "vocab": raw["vocab_size"],
+            "global_batch": args.batch,
+            "seq_len": CONTEXT,
+            "max_context": raw["max_position_embeddings"],
+            "page_size": PAGE,
+            "tied_embeddings": True,
+            "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (weights %.1f GB read every step)" % (weight_bytes / 1e9),
+            "peaks": peak_source,
+        },
+        "clocks": clocks,
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": round(achieved / hbm_gbs, 4), "bytes_per_step": int(step_bytes)},
+    }
+
+    if not args.skip_points:
+        points = {}
+        for batch in (1, 64):
+            ms, _, _ = decode_run(batch, max(10, args.steps // 2), args.warmup)
+            points[f"decode_b{batch}"] = round(batch / (ms / 1e3), 2)
+        record["points"] = points
+
+        # prefill: one 2,048-token prompt in one step, logits at its last place
+        prompt = torch.randint(0, raw["vocab_size"], (CONTEXT,), generator=gen).tolist()
+        times = []
+        for i in range(3 + 3):
+            key = f"p{i}"
+            runner.begin(key)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record()
+            runner.step([StepEntry(key, prompt, [CONTEXT - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(begin.elapsed_time(end))
+            runner.end(key)
+        ms_prefill = statistics.median(times)
+        h, q = raw["hidden_size"], raw["num_attention_heads"] * raw["head_dim"]
+        kv, inter = raw["num_key_value_heads"] * raw["head_dim"], raw["intermediate_size"]
+        linear = 2 * CONTEXT * layers * (h * (q + 2 * kv) + q * h + 3 * h * inter) + 2 * raw["vocab_size"] * h
+        attention = layers * 4 * raw["num_attention_heads"] * raw["head_dim"] * CONTEXT * (CONTEXT + 1) // 2
+        flops = linear + attention
+        record["prefill"] = {
+            "value": round(CONTEXT / (ms_prefill / 1e3), 1), "tokens": CONTEXT, "ms": round(ms_prefill, 3),
+            "frac": round(flops / (ms_prefill / 1e3) / (bf16_tflops * 1e12), 4), "flops": flops,
+        }
+
+        # end to end through the Python entry point: host ids in, sampled ids out, every step
+        del runner
+        torch.cuda.empty_cache()
+        e2e_steps = args.steps
+        engine = Engine.from_random(
+            raw, 0,
+            engine_config=EngineConfig(max_new_tokens=args.warmup + e2e_steps + 4, dtype="bfloat16"),
+            scheduler_config=SchedulerConfig(max_requests=args.batch, max_batch_size=args.batch,
+                                             token_budget=CONTEXT + args.batch, block_size=PAGE,
+                                             block_capacity=args.batch * pages_per_request + 8),
+            device=device,
+        )
+        for i in range(args.batch):
+            engine.submit(torch.randint(0, raw["vocab_size"], (CONTEXT,), generator=gen).tolist())
+        while engine.scheduler.snapshot().running < args.batch:
+            engine.step()
+        for _ in range(args.warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        produced = 0
+        for _ in range(e2e_steps):
+            produced += sum(len(e.tokens) for e in engine.step())
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+        last = engine.runner.cache
+        h2d = 4 * (args.batch * 8 + 16 + args.batch * (-(-(CONTEXT + args.warmup + e2e_steps) // PAGE)))
+        record["e2e"] = {"value": round(produced / elapsed, 2), "unit": "tokens/s",
+                         "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch,
+                         "ms_per_step": round(1e3 * elapsed / e2e_steps, 4)}
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -35,6 +35,9 @@ _ERRORS = {
 
 _lib = None
 
+# Kernel launches issued through this module since import (a claim for benchmarks).
+LAUNCHES = 0
+
 
 def lib() -> ctypes.CDLL:
     """Load (building first if needed) the kernel library exactly once."""
@@ -73,7 +76,9 @@ def has_symbol(name: str) -> bool:
 
 
 def check(code: int, what: str) -> None:
+    global LAUNCHES
     if code == 0:
+        LAUNCHES += 1
         return
     if code in _ERRORS:
         raise UnsupportedShapeError(f"{what}: {_ERRORS[code]}")

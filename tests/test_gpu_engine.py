@@ -1,0 +1,489 @@
+"""The engine in-process on the GPU: parts alone, first tokens, long decoding, generation
+through the entry point, and a toy architecture registered from this file."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import make_model_folder, random_ids
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+F32 = dict(atol=2e-5, rtol=1e-5)
+
+
+def bound(dtype: str, ref: torch.Tensor) -> dict:
+    if dtype == "float32":
+        return F32
+    return dict(atol=3e-2 * max(1.0, float(ref.abs().max())), rtol=0.0)
+
+
+@pytest.fixture(scope="module")
+def fe():
+    import forge_engine_b200
+    from forge_engine_b200.ops import native
+
+    native.require_cuda()
+    native.lib()
+    return forge_engine_b200
+
+
+def runner_for(tmp_path, raw, seed, dtype, page=8, pages=64, requests=4):
+    from forge_engine_b200.engine import ModelRunner
+
+    cfg, weights = make_model_folder(tmp_path / f"m{seed}{dtype}", raw, seed)
+    runner = ModelRunner.from_folder(tmp_path / f"m{seed}{dtype}", dtype=dtype, page_size=page,
+                                     num_pages=pages, max_requests=requests)
+    return cfg, weights, runner
+
+
+# ---------------------------------------------------------------------------
+# parts alone
+# ---------------------------------------------------------------------------
+
+def build_ctx(dtype):
+    from forge_engine_b200.parts import BuildContext
+
+    return BuildContext(dtype=dtype, device=torch.device(DEV), status=torch.zeros(1, dtype=torch.int32, device=DEV))
+
+
+def one_request_batch(cache, key, tokens, want=()):
+    from forge_engine_b200.engine import StepEntry, build_batch
+
+    cache.reserve(key, cache.request(key).length + len(tokens))
+    return build_batch([StepEntry(key, tokens, list(want))], cache, DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_and_feed_forward_parts(fe, dtype) -> None:
+    from forge_engine_b200.config import GatedMLPSpec, NormSpec
+    from forge_engine_b200.parts import build_part
+
+    ctx = build_ctx(dtype)
+    g = torch.Generator().manual_seed(0)
+    hidden, inter, n = 88, 136, 21
+    w = {"gate_proj.weight": torch.randn((inter, hidden), generator=g) * 0.1,
+         "up_proj.weight": torch.randn((inter, hidden), generator=g) * 0.1,
+         "down_proj.weight": torch.randn((hidden, inter), generator=g) * 0.1}
+    w = {k: v.bfloat16().float() for k, v in w.items()}
+    ffn = build_part(GatedMLPSpec(hidden, inter), {k: v.to(dtype).to(DEV) for k, v in w.items()}, ctx)
+    x = torch.randn((n, hidden), generator=g).bfloat16().float()
+    ref = plain.feed_forward(x, {f"p.{k}": v for k, v in w.items()}, "p")
+    out = ffn.forward(x.to(dtype).to(DEV)).float().cpu()
+    torch.testing.assert_close(out, ref, **(F32 if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)))
+
+    norm_w = 1 + 0.1 * torch.randn(hidden, generator=g)
+    norm = build_part(NormSpec(hidden, 1e-5), {"weight": norm_w.to(DEV)}, ctx)
+    res = torch.randn((n, hidden), generator=g)
+    upd = torch.randn((n, hidden), generator=g).bfloat16().float()
+    dev_res = res.clone().to(DEV)
+    out = norm.add_forward(dev_res, upd.to(dtype).to(DEV)).float().cpu()
+    torch.testing.assert_close(dev_res.cpu(), res + upd, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(out, plain.rms_norm(res + upd, norm_w, 1e-5),
+                               **(F32 if dtype == torch.float32 else dict(atol=2e-2, rtol=1e-2)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_and_block_alone(fe, dtype, window) -> None:
+    """One attention mixer and one whole block, fed in two portions, against the plain
+    functions over the whole sequence."""
+    from forge_engine_b200.cache import CacheManager
+    from forge_engine_b200.config import AttentionSpec, GatedMLPSpec, LayerSpec, NormSpec, RotarySpec
+    from forge_engine_b200.parts import arrangement_class, build_part
+
+    raw = dict(plain.TINY_C, num_hidden_layers=1)
+    if window:
+        raw.update(use_sliding_window=True, sliding_window=window, max_window_layers=0)
+    cfg = plain.PlainConfig.from_dict(raw)
+    weights = plain.seeded_weights(cfg, 9)
+    ctx = build_ctx(dtype)
+    spec = AttentionSpec(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                         True, cfg.rms_norm_eps, True, cfg.head_dim ** -0.5,
+                         RotarySpec(cfg.head_dim, cfg.rope_theta, cfg.head_dim), window)
+    prefix = "model.layers.0.self_attn"
+    local = {k[len(prefix) + 1:]: v.to(dtype).to(DEV) for k, v in weights.items() if k.startswith(prefix)}
+    mixer = build_part(spec, local, ctx)
+    cache = CacheManager([mixer.cache_needs()], page_size=4, num_pages=16, max_requests=2, dtype=dtype, device=DEV)
+    cache.begin_request("r")
+    g = torch.Generator().manual_seed(2)
+    n = 29
+    x = torch.randn((n, cfg.hidden_size), generator=g).bfloat16().float()
+    ref = plain.attention(x, weights, prefix, cfg, window)
+    outs = []
+    for lo, hi in ((0, 18), (18, 29)):
+        batch = one_request_batch(cache, "r", [0] * (hi - lo))
+        outs.append(mixer.forward(x[lo:hi].to(dtype).to(DEV), batch, cache.view(0)).float().cpu())
+        cache.advance("r", hi)
+    assert int(ctx.status.item()) == 0
+    torch.testing.assert_close(torch.cat(outs), ref, **(F32 if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)))
+
+    # the whole block: h += attn(norm(h)); returns ffn update
+    layer = LayerSpec(NormSpec(cfg.hidden_size, cfg.rms_norm_eps), spec, NormSpec(cfg.hidden_size, cfg.rms_norm_eps),
+                      GatedMLPSpec(cfg.hidden_size, cfg.intermediate_size))
+    roles = {"input_norm": "model.layers.0.input_layernorm", "mixer": prefix,
+             "post_norm": "model.layers.0.post_attention_layernorm", "ffn": "model.layers.0.mlp"}
+    block_cls = arrangement_class("pre_norm")
+    per_role = {role: {k[len(p) + 1:]: v.to(dtype).to(DEV) for k, v in weights.items() if k.startswith(p + ".")}
+                for role, p in roles.items()}
+    block = block_cls(layer, per_role, ctx)
+    cache.end_request("r")
+    cache.begin_request("r")
+    batch = one_request_batch(cache, "r", [0] * n)
+    h = x.clone().to(DEV)
+    pending = block.forward(h, None, batch, cache.view(0))
+    total = h.cpu() + pending.float().cpu()
+    ref_h = plain.decoder_layer(x, weights, 0, cfg)
+    torch.testing.assert_close(total, ref_h, **(F32 if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)))
+
+
+def test_rotary_table_is_the_plain_formula(fe) -> None:
+    from forge_engine_b200.config import RotarySpec
+    from forge_engine_b200.parts import build_part
+
+    part = build_part(RotarySpec(48, 5e6, 48), {}, build_ctx(torch.float32))
+    inv_freq, rotary_dim = part.rotary()
+    ref = 1.0 / (5e6 ** (torch.arange(0, 48, 2, dtype=torch.float32) / 48))
+    assert rotary_dim == 48 and torch.equal(inv_freq.cpu(), ref)
+
+
+# ---------------------------------------------------------------------------
+# whole model
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(fe, dtype, tmp_path) -> None:
+    """Sequences of 1, 2 and 3 tokens, and the first tokens of a longer one, alone and in
+    one batch together."""
+    from forge_engine_b200.engine import StepEntry
+
+    cfg, weights, runner = runner_for(tmp_path, plain.TINY_B, 2, dtype, page=16)
+    seqs = {f"s{n}": random_ids(cfg.vocab_size, n, 40 + n) for n in (1, 2, 3, 17)}
+    for key, ids in seqs.items():
+        runner.begin(key)
+    logits = runner.step([StepEntry(k, ids, range(len(ids))) for k, ids in seqs.items()]).cpu()
+    runner.check_status()
+    row = 0
+    for key, ids in seqs.items():
+        ref = plain.forward_logits(ids, weights, cfg)
+        torch.testing.assert_close(logits[row : row + len(ids)], ref, **bound(dtype, ref))
+        row += len(ids)
+        runner.end(key)
+    # token by token from the very first one
+    ids = seqs["s17"]
+    ref = plain.forward_logits(ids, weights, cfg)
+    runner.begin("t")
+    for i, token in enumerate(ids):
+        out = runner.step([StepEntry("t", [token], [0])]).cpu()
+        torch.testing.assert_close(out[0], ref[i], **bound(dtype, ref))
+    runner.end("t")
+    runner.cache.check_consistency()
+    assert runner.cache.leased_pages() == [0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(fe, dtype, tmp_path) -> None:
+    """A short prompt followed by several hundred single-token steps, across many pages,
+    with a windowed layer giving pages back on the way (config D)."""
+    from forge_engine_b200.engine import StepEntry
+
+    cfg, weights, runner = runner_for(tmp_path, plain.TINY_D, 6, dtype, page=4, pages=200)
+    ids = random_ids(cfg.vocab_size, 420, 8)
+    ref = plain.forward_logits(ids, weights, cfg)
+    runner.begin("a")
+    out = [runner.step([StepEntry("a", ids[:5], [4])]).cpu()[0]]
+    for token in ids[5:]:
+        out.append(runner.step([StepEntry("a", [token], [0])]).cpu()[0])
+    runner.check_status()
+    got = torch.stack(out)
+    torch.testing.assert_close(got, ref[4:], **bound(dtype, ref))
+    full, windowed = runner.cache.leased_pages()
+    assert full == 105 and windowed <= 4       # window 11 over pages of 4
+    runner.end("a")
+    assert runner.cache.leased_pages() == [0, 0]
+
+
+def test_pages_run_out_without_side_effects(fe, tmp_path) -> None:
+    from forge_engine_b200.engine import StepEntry
+    from forge_engine_b200.errors import KVCacheCapacityError
+
+    cfg, weights, runner = runner_for(tmp_path, plain.TINY_A, 0, "float32", page=4, pages=6)
+    ids = random_ids(cfg.vocab_size, 30, 3)
+    runner.begin("a"), runner.begin("b")
+    runner.step([StepEntry("a", ids[:10], [])])
+    with pytest.raises(KVCacheCapacityError):
+        runner.step([StepEntry("a", ids[10:12], [1]), StepEntry("b", ids[:13], [12])])
+    assert runner.cache.request("a").length == 10 and runner.cache.request("b").length == 0
+    assert runner.cache.leased_pages() == [3]
+    runner.cache.check_consistency()
+    out = runner.step([StepEntry("a", ids[10:12], [1])]).cpu()
+    torch.testing.assert_close(out[0], plain.forward_logits(ids[:12], weights, cfg)[11], **F32)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        runner.step([StepEntry("a", [cfg.vocab_size], [0])])
+    with pytest.raises(ValueError, match="only once"):
+        runner.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+
+
+def test_float32_checkpoint_in_bfloat16_engine_keeps_32_bit_tensors(fe, tmp_path) -> None:
+    """A tensor stored in 32-bit stays 32-bit and its products run on the plain FFMA path."""
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+
+    cfg, weights = make_model_folder(tmp_path / "m", plain.TINY_A, 0, store_dtype=torch.float32)
+    runner = ModelRunner.from_folder(tmp_path / "m", dtype="bfloat16", page_size=8, num_pages=16, max_requests=2)
+    assert runner.model.blocks[0].ffn.down.weight.dtype == torch.float32
+    ids = random_ids(cfg.vocab_size, 20, 1)
+    runner.begin("a")
+    out = runner.step([StepEntry("a", ids, range(20))]).cpu()
+    ref = plain.forward_logits(ids, weights, cfg)
+    torch.testing.assert_close(out, ref, **bound("bfloat16", ref))
+
+
+# ---------------------------------------------------------------------------
+# generation through the entry point
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_matches_plain(fe, dtype, tmp_path) -> None:
+    """Configuration A of the baseline: prompts of 5 / 9 / 13 tokens, 8 greedy tokens each,
+    page size 4; in 32-bit the ids must equal the plain implementation's exactly."""
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine
+
+    cfg, weights = make_model_folder(tmp_path / "m", dict(plain.TINY_A, eos_token_id=None), 0)
+    engine = Engine.from_pretrained(
+        tmp_path / "m",
+        engine_config=EngineConfig(max_new_tokens=8, dtype=dtype),
+        scheduler_config=SchedulerConfig(block_size=4, block_capacity=32, token_budget=16, chunk_size=6, max_batch_size=3),
+    )
+    prompts = [random_ids(cfg.vocab_size - 1, n, 1 + n) for n in (5, 9, 13)]
+    outputs = engine.generate(prompts)
+    for prompt, output in zip(prompts, outputs):
+        assert len(output) == 8
+        if dtype == "float32":
+            assert output == plain.greedy_generate(prompt, 8, weights, cfg)
+        else:
+            # bfloat16: every chosen token is the plain argmax unless the top two are nearly tied
+            ids = list(prompt)
+            for token in output:
+                ref = plain.forward_logits(ids, weights, cfg)[-1]
+                top = torch.topk(ref, 2).values
+                if float(top[0] - top[1]) > 6e-2:
+                    assert token == int(ref.argmax())
+                ids.append(token)
+    snap = engine.scheduler.snapshot()
+    assert snap.allocated_blocks == (0,) and snap.reserved_blocks == (0,)
+
+
+def test_sampled_generation_is_reproducible_and_follows_the_plain_distribution(fe, tmp_path) -> None:
+    """Configuration B of the baseline: prompts 1 / 7 / 33 / 40, portions of 8 mixed with
+    decoding, temperature 0.8.  With the kernel's uniform restated on the host, every
+    sampled id equals the draw from the plain implementation's filtered distribution."""
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine
+    from forge_engine_b200.sampling import SamplingParams
+    from test_gpu_kernels import twin_draw
+
+    cfg, weights = make_model_folder(tmp_path / "m", dict(plain.TINY_B, eos_token_id=None), 2)
+    sched = SchedulerConfig(block_size=16, block_capacity=32, token_budget=24, chunk_size=8, max_batch_size=4)
+    prompts = [random_ids(cfg.vocab_size - 2, n, 3 + n) for n in (1, 7, 33, 40)]
+    params = [SamplingParams(temperature=0.8, max_new_tokens=6, seed=4 + i, top_k=50 if i % 2 else None,
+                             top_p=0.95 if i == 2 else 1.0) for i in range(4)]
+    runs = []
+    for _ in range(2):
+        engine = Engine.from_pretrained(tmp_path / "m", engine_config=EngineConfig(dtype="float32"), scheduler_config=sched)
+        runs.append(engine.generate(prompts, params))
+    assert runs[0] == runs[1]
+    for prompt, p, output in zip(prompts, params, runs[0]):
+        ids = list(prompt)
+        for counter, token in enumerate(output):
+            ref = plain.forward_logits(ids, weights, cfg)[-1]
+            want, running, target = twin_draw(ref, p.temperature, p.top_k, p.top_p, p.min_p, p.seed, counter)
+            if token != want:
+                assert float((running - target).abs().min()) < 1e-4 * float(running[-1])
+            ids.append(token)
+
+
+def test_stream_and_cli(fe, tmp_path, capsys) -> None:
+    from forge_engine_b200.cli import main
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine
+    from forge_engine_b200.sampling import SamplingParams
+
+    cfg, weights = make_model_folder(tmp_path / "m", dict(plain.TINY_A, eos_token_id=None), 0)
+    prompt = random_ids(cfg.vocab_size - 1, 6, 5)
+    want = plain.greedy_generate(prompt, 5, weights, cfg)
+    engine = Engine.from_pretrained(tmp_path / "m", engine_config=EngineConfig(dtype="float32"),
+                                    scheduler_config=SchedulerConfig(block_size=4, block_capacity=16))
+    assert list(engine.stream(prompt, SamplingParams(max_new_tokens=5))) == want
+    stream = engine.stream(prompt, SamplingParams(max_new_tokens=5))
+    assert next(stream) == want[0]
+    stream.close()          # consumer stops early: pages still come back
+    assert engine.scheduler.snapshot().allocated_blocks == (0,)
+    code = main(["generate", "--model", str(tmp_path / "m"), "--prompt-ids", ",".join(map(str, prompt)),
+                 "--max-new-tokens", "5", "--dtype", "float32", "--block-size", "4", "--block-capacity", "16"])
+    assert code == 0
+    assert capsys.readouterr().out.strip().splitlines()[-1] == ",".join(map(str, want))
+    assert main(["generate", "--model", str(tmp_path / "nowhere"), "--prompt-ids", "1"]) == 1
+    assert "forge-engine:" in capsys.readouterr().err
+    assert main(["doctor"]) == 0
+    assert "cuda_available=True" in capsys.readouterr().out
+
+
+# ---------------------------------------------------------------------------
+# a toy architecture defined here: a mixer with state of its own, a layer named twice,
+# a run that reads another run's cache - without touching the package's files
+# ---------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class ToyDecaySpec:
+    hidden_size: int
+    decay: float
+    kind: str = "toy_decay_mixer"
+
+
+def register_toy():
+    from forge_engine_b200.cache import CacheNeeds, StateSpec
+    from forge_engine_b200.config import (Architecture, AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec,
+                                          NoPositionSpec, NormSpec, RunSpec, register_architecture)
+    from forge_engine_b200.parts import Mixer, WeightInfo, register_part
+
+    class ToyDecayMixer(Mixer):
+        """s_t = decay * s_{t-1} + x_t W^T ; y_t = s_t.  The state s is per request and of
+        fixed size; a portion continues from the state the last portion left."""
+
+        def __init__(self, spec, weights, ctx):
+            self.spec, self.w = spec, weights["w.weight"].float()
+            self.dtype = ctx.dtype
+
+        @classmethod
+        def weight_shapes(cls, spec):
+            return {"w.weight": WeightInfo((spec.hidden_size, spec.hidden_size))}
+
+        def cache_needs(self):
+            return CacheNeeds(state=StateSpec((self.spec.hidden_size,), "float32"))
+
+        def forward(self, x, batch, cache):
+            u = x.float() @ self.w.t()
+            out = torch.empty_like(u)
+            row = 0
+            for slot, start, count in batch.entries:
+                s = cache.state[slot]
+                assert start > 0 or float(s.abs().sum()) == 0.0   # a fresh slot is zeroed
+                for i in range(row, row + count):
+                    s = self.spec.decay * s + u[i]
+                    out[i] = s
+                cache.state[slot] = s
+                row += count
+            return out.to(self.dtype)
+
+    register_part("toy_decay_mixer", ToyDecayMixer, replace=True)
+
+    def spec_of(raw: dict) -> ModelSpec:
+        h = raw["hidden_size"]
+        norm = NormSpec(h, raw["eps"])
+        attn = AttentionSpec(h, 4, 2, 16, False, raw["eps"], False, 0.3, NoPositionSpec(), None)
+        ffn = GatedMLPSpec(h, raw["inter"])
+
+        def names(i):
+            return {"input_norm": f"l{i}.n1", "mixer": f"l{i}.mix", "post_norm": f"l{i}.n2", "ffn": f"l{i}.ffn"}
+
+        layers = (LayerSpec(norm, attn, norm, ffn, names(0)),
+                  LayerSpec(norm, ToyDecaySpec(h, raw["decay"]), norm, ffn, names(1)))
+        # layer 0, layer 1, layer 0 again with a cache of its own, layer 0 reading run 0's cache
+        schedule = (RunSpec(0), RunSpec(1), RunSpec(0), RunSpec(1), RunSpec(0, cache_of=0))
+        return ModelSpec(raw["vocab"], h, layers, schedule, norm, True, 4096, (), "emb.weight", "fnorm", "head.weight")
+
+    register_architecture(Architecture("ToyForCausalLM", lambda raw: raw, spec_of), replace=True)
+
+
+def toy_plain(ids, w, raw):
+    """Whole-sequence restatement of the toy model with plain torch ops."""
+    h = w["emb.weight"][torch.tensor(ids)]
+    n, eps = len(ids), raw["eps"]
+
+    def norm(x, name):
+        return plain.rms_norm(x, w[name + ".weight"], eps)
+
+    def ffn(x, p):
+        return plain.feed_forward(x, w, p)
+
+    def attn(x, p, kv_from=None):
+        q = (x @ w[p + ".q_proj.weight"].t()).view(n, 4, 16)
+        src = x if kv_from is None else kv_from
+        k = (src @ w[p + ".k_proj.weight"].t()).view(n, 2, 16).repeat_interleave(2, 1)
+        v = (src @ w[p + ".v_proj.weight"].t()).view(n, 2, 16).repeat_interleave(2, 1)
+        s = torch.einsum("thd,shd->hts", q, k) * 0.3
+        s = s + plain.causal_mask(n, s.dtype)
+        o = torch.einsum("hts,shd->thd", torch.softmax(s, -1), v).reshape(n, 64)
+        return o @ w[p + ".o_proj.weight"].t()
+
+    def decay(x, p):
+        u = x @ w[p + ".w.weight"].t()
+        out, s = [], torch.zeros(x.shape[1])
+        for i in range(n):
+            s = raw["decay"] * s + u[i]
+            out.append(s)
+        return torch.stack(out)
+
+    first_norm_input = None
+    for run, layer in enumerate((0, 1, 0, 1, 0)):
+        p = f"l{layer}"
+        x = norm(h, p + ".n1")
+        if run == 0:
+            first_norm_input = x
+        if layer == 1:
+            h = h + decay(x, p + ".mix")
+        elif run == 4:
+            h = h + attn(x, p + ".mix", kv_from=first_norm_input)   # reads run 0's keys and values
+        else:
+            h = h + attn(x, p + ".mix")
+        h = h + ffn(norm(h, p + ".n2"), p + ".ffn")
+    return norm(h, "fnorm") @ w["emb.weight"].t()
+
+
+def test_toy_architecture_registers_builds_and_steps(fe, tmp_path) -> None:
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+    from forge_engine_b200.models import expected_tensors
+    from forge_engine_b200.config import read_model_config
+    from forge_engine_b200.weights import random_tensors, write_model_folder
+
+    register_toy()
+    raw = {"architectures": ["ToyForCausalLM"], "hidden_size": 64, "inter": 72, "vocab": 97, "eps": 1e-5, "decay": 0.8}
+    _, _, spec = read_model_config(raw)
+    tensors = random_tensors(expected_tensors(spec), seed=1, std=0.1)
+    write_model_folder(tmp_path / "toy", raw, tensors)
+    runner = ModelRunner.from_folder(tmp_path / "toy", dtype="float32", page_size=4, num_pages=64, max_requests=3)
+    # two attention caches of their own (runs 0 and 2; run 4 shares run 0's), one state per decay run
+    assert [g.units for g in runner.cache.groups] == [[0, 2]]
+    assert runner.cache.state_of_run(1) is not runner.cache.state_of_run(3)
+    w = {k: v.float() for k, v in tensors.items()}
+    a, b = random_ids(97, 23, 1), random_ids(97, 14, 2)
+    ref_a, ref_b = toy_plain(a, w, raw), toy_plain(b, w, raw)
+    runner.begin("a")
+    whole = runner.step([StepEntry("a", a, range(23))]).cpu()
+    torch.testing.assert_close(whole, ref_a, atol=5e-5, rtol=1e-4)
+    runner.end("a")
+    # in portions, mixed with another request; slots are reused
+    runner.begin("b"), runner.begin("a")
+    rows_a, rows_b = [], []
+    cuts_a, cuts_b = [9, 2, 1, 11], [3, 1, 10]
+    sa = sb = 0
+    for step in range(4):
+        entries = [StepEntry("a", a[sa : sa + cuts_a[step]], range(cuts_a[step]))]
+        if step < 3:
+            entries.append(StepEntry("b", b[sb : sb + cuts_b[step]], range(cuts_b[step])))
+        out = runner.step(entries).cpu()
+        rows_a.append(out[: cuts_a[step]])
+        if step < 3:
+            rows_b.append(out[cuts_a[step] :])
+            sb += cuts_b[step]
+        sa += cuts_a[step]
+    runner.check_status()
+    torch.testing.assert_close(torch.cat(rows_a), ref_a, atol=5e-5, rtol=1e-4)
+    torch.testing.assert_close(torch.cat(rows_b), ref_b, atol=5e-5, rtol=1e-4)
+    runner.end("a"), runner.end("b")
+    runner.cache.check_consistency()
