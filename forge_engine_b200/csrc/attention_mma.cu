@@ -1,0 +1,517 @@
+// Tensor-core causal grouped-query attention over cache pages (bfloat16), compiled for
+// one head size: -DFE_HEAD_DIM=<multiple of 16, 16..256>.
+//
+// Two kernels share the tile code.  Both treat the G query heads of one kv head as extra
+// query rows (row = token * G + head_in_group), so a key/value tile is loaded once per
+// kv head and used by all its query heads.
+//
+//  * prefill: block = (64-row tile, entry, kv head); 4 warps x 16 rows; all warps walk
+//    the same 64-key tiles (double-buffered cp.async from the pages); online softmax in
+//    32-bit; handles portions that start anywhere (start > 0) and windows.
+//  * decode:  for entries with at most 16 rows (one new token, or a few): block =
+//    (split, entry, kv head); the key range is cut into `num_splits` contiguous runs of
+//    64-key tiles; inside a block each warp takes 16 keys of every tile; the four
+//    partial results are merged in shared memory and either stored (one split) or written
+//    as unnormalised (max, sum, acc) to a workspace that fe_attn_merge combines.
+//
+// Upstream's counterparts: the eager attention of src/forge_engine/qwen3.py:187-206
+// (scores, 32-bit softmax, value product) and the single-request decode kernel of
+// src/forge_engine/kernels/cuda_paged.py:276-347 (online softmax over pages).
+//
+// Rounding: scores and softmax statistics are 32-bit; probabilities are rounded to
+// bfloat16 for the value product (as upstream rounds them, qwen3.py:200); the row sum
+// uses the unrounded values.
+#include "attention_common.cuh"
+
+#ifndef FE_HEAD_DIM
+#error "compile with -DFE_HEAD_DIM=<head size>"
+#endif
+#define CAT_(a, b) a##b
+#define CAT(a, b) CAT_(a, b)
+#define SYM(name) CAT(name, FE_HEAD_DIM)
+
+namespace {
+
+constexpr int D = FE_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int LD = D + 8;          // padded row length in shared memory (elements)
+constexpr int CHUNKS = D / 8;      // 16-byte chunks per row
+constexpr int BN = 64;             // keys per tile
+constexpr int BM = 64;             // rows per prefill block
+constexpr int THREADS = 128;
+constexpr int DEC_ROWS = 16;
+
+struct AttnParams {
+  const bf16* q;
+  int q_stride;
+  bf16* out;           // [tokens, num_q_heads * D]
+  const bf16* k;
+  const bf16* v;
+  const int* block_table;
+  int max_pages, page_size, num_pages, nkv, groups;
+  const int* cu_tokens;  // [entries + 1]
+  const int* starts;     // [entries] tokens already cached before this step
+  int window;
+  float scale_log2;      // scale * log2(e)
+  int* status;
+  int row_lo, row_hi;    // the kernel handles entries with row_lo < rows <= row_hi
+  int num_splits;
+  float* ws_acc;         // [entries, nkv, splits, 16, D]
+  float* ws_ml;          // [entries, nkv, splits, 16, 2]
+};
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int size = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst)), "l"(src), "r"(size));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+
+// Stage `count` keys starting at position key0 of (entry, kv head) into dst[BN][LD].
+// Rows at or beyond key_end, and rows whose page is missing, are zero-filled.
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* base, const AttnParams& p,
+                                             const int* table, int kvh, int key0, int key_lo, int key_end,
+                                             int rows, int tid, int nthreads) {
+  for (int idx = tid; idx < rows * CHUNKS; idx += nthreads) {
+    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+    const int key = key0 + row;
+    const bf16* src = base;
+    bool valid = key < key_end && key >= 0;
+    if (valid) {
+      const int logical = key / p.page_size;
+      const int page = logical < p.max_pages ? table[logical] : -1;
+      if (page < 0 || page >= p.num_pages) {
+        valid = false;
+        if (key >= key_lo) atomicOr(p.status, FE_STATUS_BAD_PAGE);  // a key some row must see
+      } else {
+        src = base + ((((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size)) * D + chunk * 8);
+      }
+    }
+    cp_async16(dst + row * LD + chunk * 8, src, valid);
+  }
+}
+
+// One 16-row x NKEYS slice: S = Q K^T, masked online softmax, O += P V.
+//   qf    - Q fragments of this warp's 16 rows (D/16 k-steps)
+//   ks,vs - shared tiles; this warp uses keys [koff, koff + NKEYS) of them
+//   key0  - absolute position of the first of those keys
+template <int NKEYS>
+__device__ __forceinline__ void tile_step(const unsigned (&qf)[D / 16][4], const bf16* ks, const bf16* vs,
+                                          int koff, int key0, int key_end, int pos_a, int pos_b,
+                                          int window, float scale_log2, bool need_mask, float (&m)[2],
+                                          float (&l)[2], float (&o)[D / 8][4], int lane) {
+  constexpr int NT = NKEYS / 8;
+  float s[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+    for (int j2 = 0; j2 < NT / 2; ++j2) {
+      unsigned b[4];
+      const int key = koff + j2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(b, ks + key * LD + col);
+      mma_bf16(s[2 * j2], qf[kk], b[0], b[1]);
+      mma_bf16(s[2 * j2 + 1], qf[kk], b[2], b[3]);
+    }
+  }
+  const int t = lane & 3;
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float val = s[j][e] * scale_log2;
+      if (need_mask) {
+        const int key = key0 + j * 8 + 2 * t + (e & 1);
+        const int pos = (e < 2) ? pos_a : pos_b;
+        const bool seen = key <= pos && key < key_end && (window <= 0 || pos - key < window);
+        if (!seen) val = -INFINITY;
+      }
+      s[j][e] = val;
+      mx[e >> 1] = fmaxf(mx[e >> 1], val);
+    }
+  }
+  float corr[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float m_new = fmaxf(m[r], mx[r]);
+    corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - m_new);
+    m[r] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+  const float base_a = (m[0] == -INFINITY) ? 0.f : m[0];
+  const float base_b = (m[1] == -INFINITY) ? 0.f : m[1];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    s[j][0] = exp2f(s[j][0] - base_a);
+    s[j][1] = exp2f(s[j][1] - base_a);
+    s[j][2] = exp2f(s[j][2] - base_b);
+    s[j][3] = exp2f(s[j][3] - base_b);
+    sum[0] += s[j][0] + s[j][1];
+    sum[1] += s[j][2] + s[j][3];
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+    l[r] = l[r] * corr[r] + sum[r];
+  }
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) {
+    o[n][0] *= corr[0]; o[n][1] *= corr[0];
+    o[n][2] *= corr[1]; o[n][3] *= corr[1];
+  }
+#pragma unroll
+  for (int kk = 0; kk < NKEYS / 16; ++kk) {
+    unsigned a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int n2 = 0; n2 < D / 16; ++n2) {
+      unsigned b[4];
+      const int key = koff + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int col = n2 * 16 + (lane >> 4) * 8;
+      ldmatrix_x4_trans(b, vs + key * LD + col);
+      mma_bf16(o[2 * n2], a, b[0], b[1]);
+      mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Stage `rows` query rows (row = token * G + head in group) starting at row0 into qs[rows][LD].
+__device__ __forceinline__ void load_q_rows(bf16* qs, const AttnParams& p, int tok0, int kvh, int row0,
+                                            int rows_total, int rows, int tid, int nthreads) {
+  for (int idx = tid; idx < rows * CHUNKS; idx += nthreads) {
+    const int r = idx / CHUNKS, chunk = idx - r * CHUNKS;
+    const int row = row0 + r;
+    const bool valid = row < rows_total;
+    const bf16* src = p.q;
+    if (valid) {
+      const int token = row / p.groups, g = row - token * p.groups;
+      src = p.q + (size_t)(tok0 + token) * p.q_stride + (size_t)(kvh * p.groups + g) * D + chunk * 8;
+    }
+    cp_async16(qs + r * LD + chunk * 8, src, valid);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LD]
+  bf16* kbuf = qs + BM * LD;                      // [2][BN][LD]
+  bf16* vbuf = kbuf + 2 * BN * LD;                // [2][BN][LD]
+
+  const int entry = blockIdx.y, kvh = blockIdx.z;
+  const int tok0 = p.cu_tokens[entry];
+  const int n_new = p.cu_tokens[entry + 1] - tok0;
+  const int rows_total = n_new * p.groups;
+  if (rows_total <= p.row_lo || rows_total > p.row_hi) return;
+  const int row0 = blockIdx.x * BM;
+  if (row0 >= rows_total) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int start = p.starts[entry];
+  const int* table = p.block_table + (size_t)entry * p.max_pages;
+
+  const int last_row = min(rows_total, row0 + BM) - 1;
+  const int pos_first = start + row0 / p.groups;
+  const int pos_last = start + last_row / p.groups;
+  const int key_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+  const int key_end = pos_last + 1;
+  const int tile_begin = key_lo / BN, tile_end = (key_end + BN - 1) / BN;
+
+  load_q_rows(qs, p, tok0, kvh, row0, rows_total, BM, tid, THREADS);
+  load_kv_tile(kbuf, p.k, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
+  load_kv_tile(vbuf, p.v, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
+  cp_async_commit();
+
+  const int ra = row0 + warp * 16 + (lane >> 2), rb = ra + 8;
+  const int pos_a = ra < rows_total ? start + ra / p.groups : -1;
+  const int pos_b = rb < rows_total ? start + rb / p.groups : -1;
+  // positions of this warp's 16 rows, for the decision whether a tile needs masking
+  const int wrow0 = row0 + warp * 16;
+  const int wpos_min = start + min(wrow0, rows_total - 1) / p.groups;
+  const bool warp_has_padding = wrow0 + 16 > rows_total;
+  const int wpos_max = start + min(wrow0 + 15, rows_total - 1) / p.groups;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  unsigned qf[D / 16][4];
+
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    const int buf = (tile - tile_begin) & 1;
+    if (tile + 1 < tile_end) {
+      load_kv_tile(kbuf + (buf ^ 1) * BN * LD, p.k, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
+      load_kv_tile(vbuf + (buf ^ 1) * BN * LD, p.v, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (tile == tile_begin) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+    }
+    const int key0 = tile * BN;
+    // keys of this tile that no row of the warp can see are skipped altogether
+    if (wrow0 < rows_total && key0 <= wpos_max) {
+      const bool full = !warp_has_padding && key0 + BN - 1 <= wpos_min && key0 + BN <= key_end &&
+                        (p.window <= 0 || wpos_max - key0 < p.window);
+      tile_step<BN>(qf, kbuf + buf * BN * LD, vbuf + buf * BN * LD, 0, key0, key_end, pos_a, pos_b, p.window,
+                    p.scale_log2, !full, m, l, o, lane);
+    }
+    __syncthreads();
+  }
+
+  const int num_q_heads = p.nkv * p.groups;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = half ? rb : ra;
+    if (row >= rows_total) continue;
+    const int token = row / p.groups, g = row - token * p.groups;
+    const float inv = l[half] > 0.f ? 1.f / l[half] : 0.f;
+    bf16* dst = p.out + ((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const __nv_bfloat162 v2 = __floats2bfloat162_rn(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+      *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = v2;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [16][LD]
+  bf16* kbuf = qs + DEC_ROWS * LD;                // [2][BN][LD]
+  bf16* vbuf = kbuf + 2 * BN * LD;                // [2][BN][LD]
+
+  const int split = blockIdx.x, entry = blockIdx.y, kvh = blockIdx.z;
+  const int tok0 = p.cu_tokens[entry];
+  const int n_new = p.cu_tokens[entry + 1] - tok0;
+  const int rows_total = n_new * p.groups;
+  if (rows_total <= p.row_lo || rows_total > p.row_hi) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int start = p.starts[entry];
+  const int* table = p.block_table + (size_t)entry * p.max_pages;
+
+  const int pos_last = start + n_new - 1;
+  const int key_lo = p.window > 0 ? max(0, start - p.window + 1) : 0;
+  const int key_end = pos_last + 1;
+  const int tile_first = key_lo / BN, tile_stop = (key_end + BN - 1) / BN;
+  const int tiles = tile_stop - tile_first;
+  const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = tile_first + split * per_split;
+  const int tile_end = min(tile_stop, tile_begin + per_split);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+
+  const int ra = lane >> 2, rb = ra + 8;
+  const int pos_a = ra < rows_total ? start + ra / p.groups : -1;
+  const int pos_b = rb < rows_total ? start + rb / p.groups : -1;
+
+  if (tile_begin < tile_end) {
+    load_q_rows(qs, p, tok0, kvh, 0, rows_total, DEC_ROWS, tid, THREADS);
+    load_kv_tile(kbuf, p.k, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
+    load_kv_tile(vbuf, p.v, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
+    cp_async_commit();
+    unsigned qf[D / 16][4];
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+      const int buf = (tile - tile_begin) & 1;
+      if (tile + 1 < tile_end) {
+        load_kv_tile(kbuf + (buf ^ 1) * BN * LD, p.k, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
+        load_kv_tile(vbuf + (buf ^ 1) * BN * LD, p.v, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      if (tile == tile_begin) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          ldmatrix_x4(qf[kk], qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+      }
+      const int key0 = tile * BN + warp * 16;   // this warp's 16 keys of the tile
+      if (key0 < key_end)
+        tile_step<16>(qf, kbuf + buf * BN * LD, vbuf + buf * BN * LD, warp * 16, key0, key_end, pos_a, pos_b,
+                      p.window, p.scale_log2, true, m, l, o, lane);
+      __syncthreads();
+    }
+  }
+
+  // merge the four warps: reuse the (now idle) key/value buffers
+  float* acc_s = reinterpret_cast<float*>(kbuf);          // [4][16][D]
+  float* ml_s = acc_s + 4 * DEC_ROWS * D;                 // [4][16][2]
+  __syncthreads();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = half ? rb : ra;
+    float* dst = acc_s + ((size_t)warp * DEC_ROWS + row) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      dst[n * 8] = o[n][2 * half];
+      dst[n * 8 + 1] = o[n][2 * half + 1];
+    }
+    if ((lane & 3) == 0) {
+      ml_s[(warp * DEC_ROWS + row) * 2] = m[half];
+      ml_s[(warp * DEC_ROWS + row) * 2 + 1] = l[half];
+    }
+  }
+  __syncthreads();
+  const int num_q_heads = p.nkv * p.groups;
+  for (int idx = tid; idx < rows_total * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_s[(w * DEC_ROWS + row) * 2]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = ml_s[(w * DEC_ROWS + row) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - big);
+      num += acc_s[((size_t)w * DEC_ROWS + row) * D + d] * f;
+      den += ml_s[(w * DEC_ROWS + row) * 2 + 1] * f;
+    }
+    if (p.num_splits == 1) {
+      const int token = row / p.groups, g = row - token * p.groups;
+      p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
+          __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else {
+      const size_t slot = ((size_t)entry * p.nkv + kvh) * p.num_splits + split;
+      p.ws_acc[(slot * DEC_ROWS + row) * D + d] = num;
+      if (d == 0) {
+        p.ws_ml[(slot * DEC_ROWS + row) * 2] = big;
+        p.ws_ml[(slot * DEC_ROWS + row) * 2 + 1] = den;
+      }
+    }
+  }
+}
+
+// Combine the splits' (max, sum, acc) of every row: block = (entry, kv head).
+__global__ void __launch_bounds__(THREADS) attn_merge_kernel(AttnParams p) {
+  const int entry = blockIdx.x, kvh = blockIdx.y;
+  const int tok0 = p.cu_tokens[entry];
+  const int n_new = p.cu_tokens[entry + 1] - tok0;
+  const int rows_total = n_new * p.groups;
+  if (rows_total <= p.row_lo || rows_total > p.row_hi) return;
+  const int num_q_heads = p.nkv * p.groups;
+  const size_t slot0 = ((size_t)entry * p.nkv + kvh) * p.num_splits;
+  for (int idx = threadIdx.x; idx < rows_total * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float big = -INFINITY;
+    for (int s = 0; s < p.num_splits; ++s) big = fmaxf(big, p.ws_ml[((slot0 + s) * DEC_ROWS + row) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float ms = p.ws_ml[((slot0 + s) * DEC_ROWS + row) * 2];
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - big);
+      num += p.ws_acc[((slot0 + s) * DEC_ROWS + row) * D + d] * f;
+      den += p.ws_ml[((slot0 + s) * DEC_ROWS + row) * 2 + 1] * f;
+    }
+    const int token = row / p.groups, g = row - token * p.groups;
+    p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
+        __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+  }
+}
+
+constexpr size_t PREFILL_SMEM = (size_t)(BM + 4 * BN) * LD * sizeof(bf16);
+constexpr size_t DECODE_KV_SMEM = (size_t)(DEC_ROWS + 4 * BN) * LD * sizeof(bf16);
+constexpr size_t DECODE_MERGE_SMEM =
+    (size_t)DEC_ROWS * LD * sizeof(bf16) + (size_t)4 * DEC_ROWS * (D + 2) * sizeof(float);
+constexpr size_t DECODE_SMEM = DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM;
+
+}  // namespace
+
+// Workspace sizes (in floats) the decode path needs for `entries` and `num_splits`.
+FE_EXPORT long long SYM(fe_attn_workspace_floats_d)(int entries, int num_kv_heads, int num_splits) {
+  return (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
+}
+
+// mode bit 0: run the prefill kernel for entries with more than `decode_rows` rows;
+// mode bit 1: run the decode kernel (and the merge, if num_splits > 1) for the others.
+// decode_rows is 16 when the decode kernel may be used, 0 to send everything to prefill.
+FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, const void* k_cache,
+                                      const void* v_cache, const int* block_table, int max_pages,
+                                      int page_size, int num_pages, int num_kv_heads, int groups,
+                                      const int* cu_tokens, const int* starts, int entries, int max_new,
+                                      int window, float scale, int mode, int num_splits, float* workspace,
+                                      int* status, cudaStream_t stream) {
+  if (entries <= 0) return 0;
+  if (groups < 1 || groups > DEC_ROWS || num_splits < 1) return FE_ERR_BAD_SHAPE;
+  if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return FE_ERR_BAD_ALIGN;
+  if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
+  AttnParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out;
+  p.k = (const bf16*)k_cache; p.v = (const bf16*)v_cache;
+  p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.num_pages = num_pages;
+  p.nkv = num_kv_heads; p.groups = groups; p.cu_tokens = cu_tokens; p.starts = starts;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  p.num_splits = num_splits;
+  p.ws_acc = workspace;
+  p.ws_ml = workspace ? workspace + (size_t)entries * num_kv_heads * num_splits * DEC_ROWS * D : nullptr;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)PREFILL_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const bool use_decode = (mode & 2) != 0;
+  const int decode_rows = use_decode ? DEC_ROWS : 0;
+  if (mode & 1) {
+    const int max_rows = max_new * groups;
+    if (max_rows > decode_rows) {
+      p.row_lo = decode_rows; p.row_hi = 0x7fffffff;
+      dim3 grid((max_rows + BM - 1) / BM, entries, num_kv_heads);
+      attn_prefill_kernel<<<grid, THREADS, PREFILL_SMEM, stream>>>(p);
+    }
+  }
+  if (use_decode) {
+    if (num_splits > 1 && workspace == nullptr) return FE_ERR_BAD_SHAPE;
+    p.row_lo = 0; p.row_hi = DEC_ROWS;
+    dim3 grid(num_splits, entries, num_kv_heads);
+    attn_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(p);
+    if (num_splits > 1) {
+      dim3 mgrid(entries, num_kv_heads);
+      attn_merge_kernel<<<mgrid, THREADS, 0, stream>>>(p);
+    }
+  }
+  return fe_last_error();
+}

@@ -13,7 +13,7 @@ from ctypes import c_float, c_int, c_ulonglong, c_void_p
 import torch
 
 from ..errors import CUDAUnavailableError, ForgeEngineError, UnsupportedShapeError
-from .build import library_path
+from .build import attention_library_path, library_path
 
 F32, BF16 = 0, 1
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
@@ -69,6 +69,26 @@ def _declare(handle: ctypes.CDLL) -> None:
         fn.restype = c_int
     handle.fe_uniform_host.argtypes = [c_ulonglong, c_ulonglong]
     handle.fe_uniform_host.restype = c_float
+
+
+_attention_libs: dict = {}
+
+
+def attention_lib(head_dim: int):
+    """The tensor-core attention entry point compiled for ``head_dim`` (built on first use)."""
+    fn = _attention_libs.get(head_dim)
+    if fn is None:
+        path = attention_library_path(head_dim)
+        try:
+            handle = ctypes.CDLL(str(path))
+        except OSError as error:
+            raise CUDAUnavailableError(f"cannot load {path}: {error}") from error
+        fn = getattr(handle, f"fe_attention_mma_d{head_dim}")
+        p, i, f = c_void_p, c_int, c_float
+        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, f, i, i, p, p, p]
+        fn.restype = c_int
+        _attention_libs[head_dim] = fn
+    return fn
 
 
 def has_symbol(name: str) -> bool:
@@ -237,6 +257,50 @@ def attention_simt(
             stream(),
         ),
         "attention_simt",
+    )
+
+
+ATTN_DECODE_ROWS = 16  # rows (new tokens x heads per kv head) the split decode kernel takes
+
+
+def attention_mma(
+    q: torch.Tensor,
+    q_stride: int,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    cu_tokens: torch.Tensor,
+    starts: torch.Tensor,
+    entries: int,
+    max_new: int,
+    window: int | None,
+    scale: float,
+    out: torch.Tensor,
+    num_q_heads: int,
+    status: torch.Tensor,
+    run_prefill: bool,
+    run_decode: bool,
+    num_splits: int = 1,
+) -> None:
+    """Tensor-core paged attention (bfloat16).  Entries with more than 16 rows (new
+    tokens x heads per kv head) go to the prefill kernel, the others to the split
+    decode kernel; ``run_prefill`` / ``run_decode`` say which kinds the batch holds."""
+    num_pages, nkv, page_size, head_dim = k_cache.shape
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    groups = num_q_heads // nkv
+    mode = (1 if run_prefill else 0) | (2 if run_decode else 0)
+    workspace = None
+    if run_decode and num_splits > 1:
+        floats = entries * nkv * num_splits * ATTN_DECODE_ROWS * (head_dim + 2)
+        workspace = torch.empty(floats, dtype=torch.float32, device=q.device)
+    check(
+        attention_lib(head_dim)(
+            ptr(q), int(q_stride), ptr(out), ptr(k_cache), ptr(v_cache), ptr(block_table),
+            block_table.shape[1], page_size, num_pages, nkv, groups, ptr(cu_tokens), ptr(starts),
+            entries, int(max_new), int(window or 0), float(scale), mode, int(num_splits),
+            ptr(workspace), ptr(status), stream(),
+        ),
+        "attention_mma",
     )
 
 

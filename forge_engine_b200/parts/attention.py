@@ -18,6 +18,11 @@ from .base import BuildContext, CacheView, Mixer, WeightInfo, build_part, regist
 from .linear import Linear, fuse_rows
 
 
+# The split decode kernel is launched with about this many blocks (4 per SM of a B200),
+# so that few requests with long contexts still fill the machine.
+SPLIT_TARGET_BLOCKS = 592
+
+
 class GQAttention(Mixer):
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         if spec.head_dim % 16 or spec.head_dim > 256:
@@ -81,11 +86,36 @@ class GQAttention(Mixer):
             cache.owns, self.ctx.status,
         )
         out = torch.empty((x.shape[0], self.nq * self.d), dtype=qkv.dtype, device=x.device)
-        native.attention_simt(
-            qkv, qkv.shape[1], k_cache, v_cache, table, batch.positions, batch.token_entry,
-            self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
-        )
+        groups = self.nq // self.nkv
+        if qkv.dtype == torch.bfloat16 and groups <= native.ATTN_DECODE_ROWS:
+            self._tensor_core_attention(qkv, k_cache, v_cache, table, batch, out, groups)
+        else:
+            native.attention_simt(
+                qkv, qkv.shape[1], k_cache, v_cache, table, batch.positions, batch.token_entry,
+                self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
+            )
         return self.o_proj(out)
+
+    def _tensor_core_attention(self, qkv, k_cache, v_cache, table, batch, out, groups) -> None:
+        """Entries with few rows (new tokens x heads per kv head <= 16) take the split
+        decode kernel, the rest the prefill kernel; both may run in one step."""
+        limit = native.ATTN_DECODE_ROWS
+        small = [(start, count) for _, start, count in batch.entries if count * groups <= limit]
+        run_decode = bool(small)
+        run_prefill = len(small) < batch.n_entries
+        splits = 1
+        if run_decode:
+            longest = max(start + count for start, count in small)
+            if self.spec.window:
+                longest = min(longest, self.spec.window + limit)
+            tiles = -(-longest // 64)
+            blocks = len(small) * self.nkv
+            splits = max(1, min(tiles, -(-SPLIT_TARGET_BLOCKS // blocks)))
+        native.attention_mma(
+            qkv, qkv.shape[1], k_cache, v_cache, table, batch.cu_tokens, batch.starts,
+            batch.n_entries, batch.max_new, self.spec.window, self.spec.scale, out, self.nq,
+            self.ctx.status, run_prefill, run_decode, splits,
+        )
 
 
 register_part("gqa_attention", GQAttention, replace=True)

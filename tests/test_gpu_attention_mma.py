@@ -1,0 +1,97 @@
+"""The tensor-core attention kernels alone (bfloat16): prefill tiles, split decode and the
+merge, against a 64-bit dense reference on the same rounded inputs."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from test_gpu_kernels import DEV, dense_attention, paged_layout, status_word
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native():
+    from forge_engine_b200.ops import native as module
+
+    module.require_cuda()
+    module.lib()
+    return module
+
+
+def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, sharp=False):
+    """Request r holds lengths[r] keys after the step, the last new_counts[r] of them new."""
+    dtype = torch.bfloat16
+    k_cache, v_cache, table, keys, values = paged_layout(lengths, page, nkv, d, dtype, seed=d + nq + page)
+    g = torch.Generator().manual_seed(2)
+    cu, starts = [0], []
+    for n, c in zip(lengths, new_counts):
+        cu.append(cu[-1] + c)
+        starts.append(n - c)
+    total = cu[-1]
+    stride = (nq + 2 * nkv) * d          # q sits at the front of a fused qkv row, like in the engine
+    qkv = torch.randn((total, stride), generator=g).to(dtype)
+    if sharp:                            # one far key dominates one query row
+        qkv[0, :d] = (keys[0][3, 0].float() * 4).to(dtype)
+    groups = nq // nkv
+    rows = [c * groups for c in new_counts]
+    out = torch.full((total, nq * d), float("nan"), dtype=dtype, device=DEV)
+    status = status_word()
+    native.attention_mma(
+        qkv.to(DEV), stride, k_cache, v_cache, table,
+        torch.tensor(cu, dtype=torch.int32, device=DEV), torch.tensor(starts, dtype=torch.int32, device=DEV),
+        len(lengths), max(new_counts), window, d ** -0.5, out, nq, status,
+        run_prefill=any(r > 16 for r in rows), run_decode=any(r <= 16 for r in rows), num_splits=splits,
+    )
+    assert int(status.item()) == 0
+    for r, (n, c) in enumerate(zip(lengths, new_counts)):
+        q = qkv[cu[r] : cu[r + 1], : nq * d].view(c, nq, d)
+        positions = torch.arange(n - c, n)
+        ref = dense_attention(q, keys[r], values[r], positions, d ** -0.5, window)
+        mine = out[cu[r] : cu[r + 1]].view(c, nq, d).double().cpu()
+        assert torch.isfinite(mine).all()
+        torch.testing.assert_close(mine, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 2, 64, 16), (6, 3, 48, 8), (4, 2, 16, 4),
+                                           (5, 1, 32, 16), (16, 1, 256, 32), (12, 4, 80, 16)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_prefill_and_decode_mixed(native, nq, nkv, d, page, window) -> None:
+    # whole prompts, a portion that starts mid-page, single decoded tokens, a 2-token portion
+    lengths = [300, 200, 129, 1, 64, 450, 33]
+    new_counts = [300, 73, 1, 1, 2, 1, 33]
+    run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits=3, sharp=True)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+def test_split_decode_long_contexts(native, splits) -> None:
+    lengths = [2048, 1, 777, 64, 65, 4000]
+    run_case(native, 32, 8, 128, 16, None, lengths, [1] * 6, splits)
+    run_case(native, 32, 8, 128, 16, 500, lengths, [1] * 6, splits)
+
+
+def test_rows_do_not_depend_on_the_batch(native) -> None:
+    """The prefill kernel gives the same bits for a request alone and beside others."""
+    dtype = torch.bfloat16
+    nq, nkv, d, page = 8, 2, 64, 16
+    lengths, news = [200, 150, 90], [200, 150, 90]
+    k_cache, v_cache, table, keys, values = paged_layout(lengths, page, nkv, d, dtype, seed=3)
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn((sum(news), nq * d), generator=g).to(dtype).to(DEV)
+
+    def run(which):
+        cu = [0]
+        for r in which:
+            cu.append(cu[-1] + news[r])
+        rows = torch.cat([q[sum(news[:r]) : sum(news[: r + 1])] for r in which]).contiguous()
+        out = torch.empty_like(rows)
+        native.attention_mma(rows, nq * d, k_cache, v_cache, table[list(which)].contiguous(),
+                             torch.tensor(cu, dtype=torch.int32, device=DEV),
+                             torch.zeros(len(which), dtype=torch.int32, device=DEV), len(which),
+                             max(news[r] for r in which), None, d ** -0.5, out, nq, status_word(), True, False, 1)
+        return out
+
+    together = run((0, 1, 2))
+    alone = run((1,))
+    assert torch.equal(together[200:350], alone)
