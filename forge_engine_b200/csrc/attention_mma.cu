@@ -21,6 +21,8 @@
 // Rounding: scores and softmax statistics are 32-bit; probabilities are rounded to
 // bfloat16 for the value product (as upstream rounds them, qwen3.py:200); the row sum
 // uses the unrounded values.
+#include <stdio.h>
+
 #include "attention_common.cuh"
 
 #ifndef FE_HEAD_DIM
@@ -512,6 +514,74 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
       dim3 mgrid(entries, num_kv_heads);
       attn_merge_kernel<<<mgrid, THREADS, 0, stream>>>(p);
     }
+  }
+  return fe_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// Split decode attention for callers that must not allocate (see attention_noalloc.h).
+// No counterpart upstream.
+// ---------------------------------------------------------------------------
+
+// Scratch for the splits' partial results, held by every GPU that loads this library
+// until the process exits: 1,048,576 floats = 4 MiB.
+#define FE_NOALLOC_SCRATCH_FLOATS (1 << 20)
+static __device__ __align__(256) float fe_noalloc_scratch[FE_NOALLOC_SCRATCH_FLOATS];
+
+#define FE_ERR_SCRATCH_TOO_SMALL 10005
+#define FE_NOALLOC_MAX_DEVICES 64
+
+FE_EXPORT int SYM(fe_attention_decode_noalloc_d)(const void* q, int q_stride, void* out,
+                                                 const void* k_cache, const void* v_cache,
+                                                 const int* block_table, int max_pages, int page_size,
+                                                 int num_pages, int num_kv_heads, int groups,
+                                                 const int* cu_tokens, const int* starts, int entries,
+                                                 int max_new, int window, float scale, int num_splits,
+                                                 int* status, cudaStream_t stream) {
+  // Device address of the scratch array, looked up once per device.  In host code the
+  // array's name is only a handle for the runtime, not a pointer a kernel could use.
+  static float* scratch_of_device[FE_NOALLOC_MAX_DEVICES] = {nullptr};
+  if (entries <= 0) return 0;
+  if (groups < 1 || num_splits < 1 || max_new < 1 || max_new * groups > DEC_ROWS) return FE_ERR_BAD_SHAPE;
+  if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return FE_ERR_BAD_ALIGN;
+  if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
+  const long long needed = (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
+  if (needed > FE_NOALLOC_SCRATCH_FLOATS) {
+    fprintf(stderr,
+            "fe_attention_decode_noalloc: entries=%d x kv_heads=%d x splits=%d needs %lld floats of scratch, "
+            "the built-in array holds %d; use fewer splits or fewer entries per call\n",
+            entries, num_kv_heads, num_splits, needed, FE_NOALLOC_SCRATCH_FLOATS);
+    return FE_ERR_SCRATCH_TOO_SMALL;
+  }
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= FE_NOALLOC_MAX_DEVICES) return FE_ERR_TOO_LARGE;
+  if (scratch_of_device[device] == nullptr) {
+    float* address = nullptr;
+    e = cudaGetSymbolAddress((void**)&address, fe_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    scratch_of_device[device] = address;
+  }
+  float* scratch = scratch_of_device[device];
+  AttnParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out;
+  p.k = (const bf16*)k_cache; p.v = (const bf16*)v_cache;
+  p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.num_pages = num_pages;
+  p.nkv = num_kv_heads; p.groups = groups; p.cu_tokens = cu_tokens; p.starts = starts;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  p.num_splits = num_splits;
+  p.ws_acc = scratch;
+  p.ws_ml = scratch + (size_t)entries * num_kv_heads * num_splits * DEC_ROWS * D;
+  p.row_lo = 0; p.row_hi = DEC_ROWS;
+  dim3 grid(num_splits, entries, num_kv_heads);
+  attn_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(p);
+  if (num_splits > 1) {
+    dim3 mgrid(entries, num_kv_heads);
+    attn_merge_kernel<<<mgrid, THREADS, 0, stream>>>(p);
   }
   return fe_last_error();
 }

@@ -1,0 +1,89 @@
+"""The allocation-free decode attention entry point, called through its exported C symbol.
+
+Programs that embed the kernel library without torch (or that have given all device
+memory to an allocator of their own, or cannot afford cudaMalloc's device-wide stall in a
+serving loop) call ``fe_attention_decode_noalloc_d<HEAD>``: its scratch is an array inside
+the library.  Here it is loaded with ctypes exactly as such a program would, and its output
+is compared with the usual entry point's (which gets a workspace from the caller) on two
+calls in a row with different inputs, so that whatever the first call left in the shared
+scratch is shown not to matter.  This file sorts last on purpose: a run that stops at the
+first failure has then already run every other test.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import pytest
+import torch
+
+from test_gpu_kernels import DEV, dense_attention, paged_layout, status_word
+
+pytestmark = pytest.mark.gpu
+
+HEAD = 128
+
+
+def load_symbol():
+    from forge_engine_b200.ops import native
+    from forge_engine_b200.ops.build import attention_library_path
+
+    native.require_cuda()
+    handle = ctypes.CDLL(str(attention_library_path(HEAD)))
+    fn = getattr(handle, f"fe_attention_decode_noalloc_d{HEAD}")
+    p, i = c_void_p, c_int
+    fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, c_float, i, p, p]
+    fn.restype = c_int
+    return fn
+
+
+def call_both(fn, seed: int, lengths: list, splits: int, window: int):
+    from forge_engine_b200.ops import native
+
+    nq, nkv, page = 32, 8, 16
+    k_cache, v_cache, table, keys, values = paged_layout(lengths, page, nkv, HEAD, torch.bfloat16, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    entries = len(lengths)
+    q = torch.randn((entries, nq * HEAD), generator=g).to(torch.bfloat16).to(DEV)
+    cu = torch.arange(entries + 1, dtype=torch.int32, device=DEV)
+    starts = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    scale = HEAD ** -0.5
+    usual = torch.empty((entries, nq * HEAD), dtype=torch.bfloat16, device=DEV)
+    status = status_word()
+    native.attention_mma(q, nq * HEAD, k_cache, v_cache, table, cu, starts, entries, 1, window, scale, usual,
+                         nq, status, run_prefill=False, run_decode=True, num_splits=splits)
+    mine = torch.full_like(usual, float("nan"))
+    code = fn(q.data_ptr(), nq * HEAD, mine.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(),
+              table.shape[1], page, k_cache.shape[0], nkv, nq // nkv, cu.data_ptr(), starts.data_ptr(), entries, 1,
+              window, scale, splits, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert code == 0 and int(status.item()) == 0
+    # against the usual entry point: the same kernels on the same inputs, so the same numbers
+    torch.testing.assert_close(mine.float(), usual.float(), atol=2e-2, rtol=2e-2)
+    # and against the dense 64-bit reference, with the tolerance of the other attention tests
+    for r, n in enumerate(lengths):
+        ref = dense_attention(q[r].cpu().view(1, nq, HEAD), keys[r], values[r], torch.tensor([n - 1]), scale, window)
+        torch.testing.assert_close(mine[r].double().cpu().view(1, nq, HEAD), ref, atol=2e-2, rtol=2e-2)
+    return mine
+
+
+def test_no_alloc_entry_matches_the_usual_one_twice_in_a_row() -> None:
+    fn = load_symbol()
+    before = torch.cuda.memory_allocated()
+    first = call_both(fn, 11, [700, 64, 1, 2048], splits=6, window=0)
+    second = call_both(fn, 23, [1500, 333, 65], splits=9, window=400)   # other sizes over the leftovers
+    assert first.shape != second.shape
+    assert torch.cuda.memory_allocated() <= before + 64 * 2**20
+
+
+def test_no_alloc_entry_refuses_what_does_not_fit() -> None:
+    fn = load_symbol()
+    dummy = torch.zeros(64, dtype=torch.int32, device=DEV)
+    aligned = torch.zeros(4096, dtype=torch.bfloat16, device=DEV)
+    args = lambda entries, splits, max_new=1: (  # noqa: E731
+        aligned.data_ptr(), 4096, aligned.data_ptr(), aligned.data_ptr(), aligned.data_ptr(), dummy.data_ptr(), 1, 16,
+        1, 8, 4, dummy.data_ptr(), dummy.data_ptr(), entries, max_new, 0, 0.1, splits, dummy.data_ptr(), 0)
+    assert fn(*args(64, 8)) == 10005       # 64 * 8 * 8 * 16 * 130 floats > 1,048,576
+    assert fn(*args(1, 1, max_new=5)) == 10002   # 5 tokens x 4 heads = 20 rows: not a decode shape
+    torch.cuda.synchronize()
