@@ -99,6 +99,7 @@ class CacheManager:
         self.dtype = dtype
         self.device = device
         self.shares = dict(shares or {})
+        self.null_page = num_pages
         self.slots = StateSlots(max_requests)
         self.groups: list[LayerGroup] = []
         self._run_group: dict[int, tuple] = {}  # run -> (group index, unit slot)
@@ -135,8 +136,10 @@ class CacheManager:
 
         for group in self.groups:
             spec = group.spec
+            # one page more than the pool leases: ``null_page`` takes the keys of filler
+            # entries of fixed-size (graph-replayed) batches and is never read back
             group.storage = torch.zeros(
-                (len(group.units), 2, self.num_pages, spec.num_kv_heads, self.page_size, spec.head_dim),
+                (len(group.units), 2, self.num_pages + 1, spec.num_kv_heads, self.page_size, spec.head_dim),
                 dtype=self.dtype,
                 device=self.device,
             )

@@ -93,27 +93,39 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&h);
 }
 
-// Stage `count` keys starting at position key0 of (entry, kv head) into dst[BN][LD].
-// Rows at or beyond key_end, and rows whose page is missing, are zero-filled.
-__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* base, const AttnParams& p,
-                                             const int* table, int kvh, int key0, int key_lo, int key_end,
-                                             int rows, int tid, int nthreads) {
-  for (int idx = tid; idx < rows * CHUNKS; idx += nthreads) {
-    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
-    const int key = key0 + row;
-    const bf16* src = base;
-    bool valid = key < key_end && key >= 0;
-    if (valid) {
-      const int logical = key / p.page_size;
-      const int page = logical < p.max_pages ? table[logical] : -1;
-      if (page < 0 || page >= p.num_pages) {
-        valid = false;
-        if (key >= key_lo) atomicOr(p.status, FE_STATUS_BAD_PAGE);  // a key some row must see
-      } else {
-        src = base + ((((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size)) * D + chunk * 8);
-      }
+// Stage keys [key0, key0 + BN) of (entry, kv head) into kdst[BN][LD] and their values into
+// vdst[BN][LD].  Rows at or beyond key_end, and rows whose page is missing, are zero-filled.
+// A thread looks its row's page up once and then issues that row's 16-byte copies for
+// both matrices, so the address arithmetic is paid per row, not per copy.
+__device__ __forceinline__ void load_kv_tile(bf16* kdst, bf16* vdst, const AttnParams& p, const int* table,
+                                             int kvh, int key0, int key_lo, int key_end, int tid) {
+  constexpr int PARTS = THREADS / BN;              // threads per row
+  constexpr int PER = (CHUNKS + PARTS - 1) / PARTS;  // chunks per thread and matrix
+  const int row = tid / PARTS, part = tid - row * PARTS;
+  const int key = key0 + row;
+  size_t offset = 0;
+  bool valid = key < key_end && key >= 0;
+  if (valid) {
+    const int logical = key / p.page_size;
+    const int page = logical < p.max_pages ? table[logical] : -1;
+    if (page < 0 || page >= p.num_pages) {
+      valid = false;
+      if (key >= key_lo) atomicOr(p.status, FE_STATUS_BAD_PAGE);  // a key some row must see
+    } else {
+      offset = (((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size)) * D;
     }
-    cp_async16(dst + row * LD + chunk * 8, src, valid);
+  }
+  const bf16* ksrc = p.k + offset;
+  const bf16* vsrc = p.v + offset;
+  bf16* kd = kdst + row * LD;
+  bf16* vd = vdst + row * LD;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int chunk = part + i * PARTS;     // neighbouring threads take neighbouring chunks
+    if (chunk < CHUNKS) {
+      cp_async16(kd + chunk * 8, ksrc + chunk * 8, valid);
+      cp_async16(vd + chunk * 8, vsrc + chunk * 8, valid);
+    }
   }
 }
 
@@ -251,8 +263,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   const int tile_begin = key_lo / BN, tile_end = (key_end + BN - 1) / BN;
 
   load_q_rows(qs, p, tok0, kvh, row0, rows_total, BM, tid, THREADS);
-  load_kv_tile(kbuf, p.k, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
-  load_kv_tile(vbuf, p.v, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
+  load_kv_tile(kbuf, vbuf, p, table, kvh, tile_begin * BN, key_lo, key_end, tid);
   cp_async_commit();
 
   const int ra = row0 + warp * 16 + (lane >> 2), rb = ra + 8;
@@ -273,8 +284,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int buf = (tile - tile_begin) & 1;
     if (tile + 1 < tile_end) {
-      load_kv_tile(kbuf + (buf ^ 1) * BN * LD, p.k, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
-      load_kv_tile(vbuf + (buf ^ 1) * BN * LD, p.v, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
+      load_kv_tile(kbuf + (buf ^ 1) * BN * LD, vbuf + (buf ^ 1) * BN * LD, p, table, kvh, (tile + 1) * BN, key_lo,
+                   key_end, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -348,15 +359,14 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
 
   if (tile_begin < tile_end) {
     load_q_rows(qs, p, tok0, kvh, 0, rows_total, DEC_ROWS, tid, THREADS);
-    load_kv_tile(kbuf, p.k, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
-    load_kv_tile(vbuf, p.v, p, table, kvh, tile_begin * BN, key_lo, key_end, BN, tid, THREADS);
+    load_kv_tile(kbuf, vbuf, p, table, kvh, tile_begin * BN, key_lo, key_end, tid);
     cp_async_commit();
     unsigned qf[D / 16][4];
     for (int tile = tile_begin; tile < tile_end; ++tile) {
       const int buf = (tile - tile_begin) & 1;
       if (tile + 1 < tile_end) {
-        load_kv_tile(kbuf + (buf ^ 1) * BN * LD, p.k, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
-        load_kv_tile(vbuf + (buf ^ 1) * BN * LD, p.v, p, table, kvh, (tile + 1) * BN, key_lo, key_end, BN, tid, THREADS);
+        load_kv_tile(kbuf + (buf ^ 1) * BN * LD, vbuf + (buf ^ 1) * BN * LD, p, table, kvh, (tile + 1) * BN,
+                     key_lo, key_end, tid);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
@@ -424,29 +434,59 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
   }
 }
 
-// Combine the splits' (max, sum, acc) of every row: block = (entry, kv head).
+// Combine the splits' (max, sum, acc) of every row: block = (entry, kv head).  The splits'
+// weights exp2(m_s - max) / sum are worked out once per row in shared memory; then every
+// thread owns one or more columns and sums over the splits with independent loads.
+constexpr int MERGE_MAX_SPLITS = 64;
+
 __global__ void __launch_bounds__(THREADS) attn_merge_kernel(AttnParams p) {
+  __shared__ float weight_s[DEC_ROWS][MERGE_MAX_SPLITS];
   const int entry = blockIdx.x, kvh = blockIdx.y;
   const int tok0 = p.cu_tokens[entry];
   const int n_new = p.cu_tokens[entry + 1] - tok0;
   const int rows_total = n_new * p.groups;
   if (rows_total <= p.row_lo || rows_total > p.row_hi) return;
   const int num_q_heads = p.nkv * p.groups;
-  const size_t slot0 = ((size_t)entry * p.nkv + kvh) * p.num_splits;
+  const int splits = p.num_splits;
+  const size_t slot0 = ((size_t)entry * p.nkv + kvh) * splits;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = warp; row < rows_total; row += THREADS / 32) {
+    float mv[MERGE_MAX_SPLITS / 32], lv[MERGE_MAX_SPLITS / 32];
+    float big = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int s = lane + i * 32;
+      mv[i] = -INFINITY; lv[i] = 0.f;
+      if (s < splits) {
+        const float2 ml = *reinterpret_cast<const float2*>(p.ws_ml + ((slot0 + s) * DEC_ROWS + row) * 2);
+        mv[i] = ml.x; lv[i] = ml.y;
+      }
+      big = fmaxf(big, mv[i]);
+    }
+    big = warp_max(big);
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      mv[i] = (mv[i] == -INFINITY) ? 0.f : exp2f(mv[i] - big);
+      den += lv[i] * mv[i];
+    }
+    den = warp_sum(den);
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int s = lane + i * 32;
+      if (s < splits) weight_s[row][s] = mv[i] * inv;
+    }
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < rows_total * D; idx += THREADS) {
     const int row = idx / D, d = idx - row * D;
-    float big = -INFINITY;
-    for (int s = 0; s < p.num_splits; ++s) big = fmaxf(big, p.ws_ml[((slot0 + s) * DEC_ROWS + row) * 2]);
-    float num = 0.f, den = 0.f;
-    for (int s = 0; s < p.num_splits; ++s) {
-      const float ms = p.ws_ml[((slot0 + s) * DEC_ROWS + row) * 2];
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - big);
-      num += p.ws_acc[((slot0 + s) * DEC_ROWS + row) * D + d] * f;
-      den += p.ws_ml[((slot0 + s) * DEC_ROWS + row) * 2 + 1] * f;
-    }
+    const float* src = p.ws_acc + (slot0 * DEC_ROWS + row) * D + d;
+    float num = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) num += src[(size_t)s * DEC_ROWS * D] * weight_s[row][s];
     const int token = row / p.groups, g = row - token * p.groups;
-    p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
-        __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] = __float2bfloat16_rn(num);
   }
 }
 
@@ -473,7 +513,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
                                       int window, float scale, int mode, int num_splits, float* workspace,
                                       int* status, cudaStream_t stream) {
   if (entries <= 0) return 0;
-  if (groups < 1 || groups > DEC_ROWS || num_splits < 1) return FE_ERR_BAD_SHAPE;
+  if (groups < 1 || groups > DEC_ROWS || num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return FE_ERR_BAD_SHAPE;
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return FE_ERR_BAD_ALIGN;
   if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
@@ -542,7 +582,8 @@ FE_EXPORT int SYM(fe_attention_decode_noalloc_d)(const void* q, int q_stride, vo
   // array's name is only a handle for the runtime, not a pointer a kernel could use.
   static float* scratch_of_device[FE_NOALLOC_MAX_DEVICES] = {nullptr};
   if (entries <= 0) return 0;
-  if (groups < 1 || num_splits < 1 || max_new < 1 || max_new * groups > DEC_ROWS) return FE_ERR_BAD_SHAPE;
+  if (groups < 1 || num_splits < 1 || num_splits > MERGE_MAX_SPLITS || max_new < 1 || max_new * groups > DEC_ROWS)
+    return FE_ERR_BAD_SHAPE;
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return FE_ERR_BAD_ALIGN;
   if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;

@@ -42,30 +42,53 @@ FE_EXPORT int fe_embedding(const int* ids, const void* table, int table_dtype, f
 // out[r] = x * rsqrt(mean(x^2) + eps) * weight       -- all in 32-bit, one rounding
 // src = row_map ? row_map[r] : r
 // ---------------------------------------------------------------------------
-template <typename TU, typename TO>
+template <typename TU, typename TO, int PER>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ update,
                                    const float* __restrict__ weight, TO* __restrict__ out,
                                    const int* __restrict__ row_map, int size, float eps,
                                    int write_residual) {
+  // PER > 0: every thread keeps its PER elements (strided by blockDim) in registers between
+  // the two passes; PER == 0: rows too long for that are read twice.
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int src = row_map ? row_map[r] : r;
   float* res = residual + (size_t)src * size;
   const TU* upd = update ? update + (size_t)src * size : nullptr;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < size; i += blockDim.x) {
-    float x = res[i];
-    if (upd) x += to_float(upd[i]);
-    if (write_residual) res[i] = x;
-    ss += x * x;
-  }
-  const float total = block_sum(ss, scratch);
-  const float inv = rsqrtf(total / (float)size + eps);
   TO* dst = out + (size_t)r * size;
-  for (int i = threadIdx.x; i < size; i += blockDim.x) {
-    float x = res[i];
-    if (upd && !write_residual) x += to_float(upd[i]);
-    dst[i] = from_float<TO>(x * inv * weight[i]);
+  float ss = 0.f;
+  if constexpr (PER > 0) {
+    float x[PER > 0 ? PER : 1];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      x[j] = 0.f;
+      if (i < size) {
+        x[j] = res[i];
+        if (upd) x[j] += to_float(upd[i]);
+        if (write_residual) res[i] = x[j];
+        ss += x[j] * x[j];
+      }
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)size + eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < size) dst[i] = from_float<TO>(x[j] * inv * weight[i]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+      float x = res[i];
+      if (upd) x += to_float(upd[i]);
+      if (write_residual) res[i] = x;
+      ss += x * x;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)size + eps);
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+      float x = res[i];
+      if (upd && !write_residual) x += to_float(upd[i]);
+      dst[i] = from_float<TO>(x * inv * weight[i]);
+    }
   }
 }
 
@@ -76,9 +99,19 @@ FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dty
   if (rows <= 0) return 0;
   int threads = 32;
   while (threads < 512 && threads * 4 < size) threads <<= 1;
-#define LAUNCH(TU, TO)                                                                  \
-  add_rmsnorm_kernel<TU, TO><<<rows, threads, 0, stream>>>(residual, (const TU*)update, \
-      weight, (TO*)out, row_map, size, eps, write_residual)
+  const int per = (size + threads - 1) / threads;
+#define LAUNCH(TU, TO)                                                                               \
+  do {                                                                                               \
+    if (per <= 4)                                                                                    \
+      add_rmsnorm_kernel<TU, TO, 4><<<rows, threads, 0, stream>>>(residual, (const TU*)update,      \
+          weight, (TO*)out, row_map, size, eps, write_residual);                                     \
+    else if (per <= 16)                                                                              \
+      add_rmsnorm_kernel<TU, TO, 16><<<rows, threads, 0, stream>>>(residual, (const TU*)update,     \
+          weight, (TO*)out, row_map, size, eps, write_residual);                                     \
+    else                                                                                             \
+      add_rmsnorm_kernel<TU, TO, 0><<<rows, threads, 0, stream>>>(residual, (const TU*)update,      \
+          weight, (TO*)out, row_map, size, eps, write_residual);                                     \
+  } while (0)
   if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH(float, float);
   else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH(bf16, bf16);
   else if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) LAUNCH(float, bf16);

@@ -19,8 +19,9 @@ __global__ void qk_rope_cache_kernel(T* __restrict__ qkv, const float* __restric
                                      const int* __restrict__ token_entry, PagedKV cache,
                                      int num_q_heads, int write_kv, int* status) {
   const int token = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int warps = (blockDim.x >> 5) * gridDim.y;             // warps working on this token
+  const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int D = cache.head_dim, nkv = cache.num_kv_heads;
   const int heads_total = num_q_heads + 2 * nkv;
   const int pos = positions[token];
@@ -32,11 +33,11 @@ __global__ void qk_rope_cache_kernel(T* __restrict__ qkv, const float* __restric
     const int logical = pos / cache.page_size;
     slot = pos - logical * cache.page_size;
     if (pos < 0 || logical >= cache.max_pages) {
-      if (threadIdx.x == 0) atomicOr(status, FE_STATUS_BAD_POSITION);
+      if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, FE_STATUS_BAD_POSITION);
     } else {
       page = cache.block_table[(size_t)entry * cache.max_pages + logical];
       if (page < 0 || page >= cache.num_pages) {
-        if (threadIdx.x == 0) atomicOr(status, FE_STATUS_BAD_PAGE);
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, FE_STATUS_BAD_PAGE);
         page = -1;
       }
     }
@@ -103,12 +104,19 @@ FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, cons
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return FE_ERR_BAD_SHAPE;
   PagedKV cache{k_cache, v_cache, block_table, max_pages, page_size, num_pages, num_kv_heads, head_dim};
   const int heads_total = num_q_heads + 2 * num_kv_heads;
-  int warps = heads_total < 8 ? heads_total : 8;
+  // one warp per head while the batch is small (latency matters), up to 8 heads per warp
+  // when there are many tokens
+  int per_warp = n_tokens >= 512 ? 8 : (n_tokens >= 64 ? 2 : 1);
+  const int warps_needed = (heads_total + per_warp - 1) / per_warp;
+  const int warps = warps_needed < 4 ? warps_needed : 4;
+  const int blocks_y = (warps_needed + warps - 1) / warps;
+  if (blocks_y > 65535) return FE_ERR_TOO_LARGE;
+  dim3 grid(n_tokens, blocks_y);
   if (dtype == FE_DTYPE_F32)
-    qk_rope_cache_kernel<float><<<n_tokens, warps * 32, 0, stream>>>((float*)qkv, q_weight, k_weight,
+    qk_rope_cache_kernel<float><<<grid, warps * 32, 0, stream>>>((float*)qkv, q_weight, k_weight,
         eps, inv_freq, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
   else if (dtype == FE_DTYPE_BF16)
-    qk_rope_cache_kernel<bf16><<<n_tokens, warps * 32, 0, stream>>>((bf16*)qkv, q_weight, k_weight,
+    qk_rope_cache_kernel<bf16><<<grid, warps * 32, 0, stream>>>((bf16*)qkv, q_weight, k_weight,
         eps, inv_freq, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
   else
     return FE_ERR_BAD_DTYPE;

@@ -53,8 +53,29 @@ class StepBatch:
     max_ctx: int = 0
 
 
-def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
-    """Lay out the step's integers.  Pages for the new tokens must already be reserved."""
+@dataclass
+class BatchPlan:
+    """The integers of a step laid out in one flat host array, before any copy."""
+
+    flat: list
+    offsets: dict          # name -> (begin, length)
+    n_tokens: int
+    n_entries: int
+    n_want: int
+    table_widths: list
+    entries: list          # (slot, start, count) per entry
+    max_new: int
+    max_ctx: int
+
+
+def plan_batch(entries: Sequence[StepEntry], cache, *, pad_entries: int = 0, table_width: int | None = None,
+               null_page: int | None = None) -> BatchPlan:
+    """Lay out the step's integers.  Pages for the new tokens must already be reserved.
+
+    ``pad_entries`` appends that many filler entries (one token at position 0 whose keys
+    go to ``null_page``, a page no request ever holds) so that the batch has a fixed
+    number of entries; ``table_width`` fixes the width of every block table.  Both are
+    used by replayed CUDA graphs, whose kernels are launched with fixed sizes."""
     token_ids: list[int] = []
     positions: list[int] = []
     token_entry: list[int] = []
@@ -78,15 +99,31 @@ def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
         ctx_lens.append(start + count)
         slots.append(request.slot)
         host.append((request.slot, start, count))
-    n, r = cu[-1], len(entries)
+    for pad in range(pad_entries):
+        token_ids.append(0)
+        positions.append(0)
+        token_entry.append(len(entries) + pad)
+        want_rows.append(cu[-1])
+        cu.append(cu[-1] + 1)
+        starts.append(0)
+        ctx_lens.append(1)
+        slots.append(0)
+    n, r = cu[-1], len(entries) + pad_entries
     tables = []
     for g in range(len(cache.groups)):
-        width = max(1, max(len(req.tables[g].pages) for req in requests))
+        width = max(1, max((len(req.tables[g].pages) for req in requests), default=1))
+        if table_width is not None:
+            if width > table_width:
+                raise ValueError("a block table is wider than the fixed width")
+            width = table_width
         rows = []
         for req in requests:
             pages = req.tables[g].pages
             rows.extend(pages)
             rows.extend([-1] * (width - len(pages)))
+        for _ in range(pad_entries):
+            rows.append(null_page)
+            rows.extend([-1] * (width - 1))
         tables.append((width, rows))
     flat: list[int] = []
     offsets = {}
@@ -106,19 +143,21 @@ def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
     put("want_rows", want_rows)
     for g, (_, rows) in enumerate(tables):
         put(f"table{g}", rows)
-    host_buffer = torch.tensor(flat, dtype=torch.int32)
-    if torch.device(device).type == "cuda":
-        host_buffer = host_buffer.pin_memory()
-    device_buffer = host_buffer.to(device, non_blocking=True)
+    return BatchPlan(flat, offsets, n, r, len(want_rows), [w for w, _ in tables], host,
+                     max((c for _, _, c in host), default=1), max(ctx_lens))
+
+
+def batch_from_buffer(plan: BatchPlan, device_buffer: torch.Tensor) -> StepBatch:
+    """Views of ``device_buffer`` (which holds ``plan.flat``) as a StepBatch."""
 
     def view(name: str) -> torch.Tensor:
-        begin, length = offsets[name]
+        begin, length = plan.offsets[name]
         return device_buffer[begin : begin + length]
 
     return StepBatch(
-        n_tokens=n,
-        n_entries=r,
-        n_want=len(want_rows),
+        n_tokens=plan.n_tokens,
+        n_entries=plan.n_entries,
+        n_want=plan.n_want,
         token_ids=view("token_ids"),
         positions=view("positions"),
         token_entry=view("token_entry"),
@@ -127,8 +166,22 @@ def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
         ctx_lens=view("ctx_lens"),
         slots=view("slots"),
         want_rows=view("want_rows"),
-        group_tables=[view(f"table{g}").view(r, tables[g][0]) for g in range(len(tables))],
-        entries=host,
-        max_new=max(c for _, _, c in host),
-        max_ctx=max(ctx_lens),
+        group_tables=[view(f"table{g}").view(plan.n_entries, w) for g, w in enumerate(plan.table_widths)],
+        entries=plan.entries,
+        max_new=plan.max_new,
+        max_ctx=plan.max_ctx,
     )
+
+
+def upload(flat: list, device) -> torch.Tensor:
+    """One pinned host tensor, one asynchronous copy."""
+    host_buffer = torch.tensor(flat, dtype=torch.int32)
+    if torch.device(device).type == "cuda":
+        host_buffer = host_buffer.pin_memory()
+    return host_buffer.to(device, non_blocking=True)
+
+
+def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
+    """Plan, upload and view a step's batch."""
+    plan = plan_batch(entries, cache)
+    return batch_from_buffer(plan, upload(plan.flat, device))

@@ -1,0 +1,108 @@
+"""CUDA graphs for decode steps.
+
+A decode step at small batch is a few hundred short kernels; issued one by one from
+Python they take longer to launch than to run.  Upstream launches everything eagerly and
+even synchronises per token (src/forge_engine/engine.py:425).  Here a step in which every
+entry brings exactly one token is captured once per *bucket* - (entries rounded up to a
+power of two, block-table width rounded up to a power of two) - and replayed: the
+step's integers are copied into the graph's fixed device buffer, filler entries pad the
+batch to the bucket's size (their keys go to the cache's null page), and the kernels run
+with the sizes they were captured with.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import native
+from .batch import BatchPlan, batch_from_buffer, plan_batch
+
+
+def _bucket(value: int, floor: int = 1) -> int:
+    size = floor
+    while size < value:
+        size *= 2
+    return size
+
+
+class _CapturedStep:
+    def __init__(self, graph, buffer, logits, launches) -> None:
+        self.graph = graph
+        self.buffer = buffer
+        self.logits = logits
+        self.launches = launches
+
+
+class DecodeGraphs:
+    """Captures and replays decode steps of one ModelRunner."""
+
+    def __init__(self, model, cache, max_entries: int) -> None:
+        self.model = model
+        self.cache = cache
+        self.max_entries = max_entries
+        self.captured: dict[tuple, _CapturedStep] = {}
+        self.pool = None
+
+    def usable(self) -> bool:
+        return all(getattr(block.mixer, "graph_safe", False) for block in self.model.blocks)
+
+    def _plan(self, entries, bucket_entries: int, width: int) -> BatchPlan:
+        return plan_batch(entries, self.cache, pad_entries=bucket_entries - len(entries), table_width=width,
+                          null_page=self.cache.null_page)
+
+    def _capture(self, key: tuple) -> _CapturedStep:
+        bucket_entries, width = key
+        device = self.model.ctx.device
+        page = self.cache.page_size
+        # A batch of filler entries only: it has the bucket's layout and is safe to run.
+        plan = self._plan([], bucket_entries, width)
+        # The capture sees host-side entries that all sit at the bucket's longest context,
+        # so that size decisions made on the host (attention splits) fit every step that
+        # will be replayed with this graph.
+        plan.entries = [(0, width * page - 1, 1)] * bucket_entries
+        plan.max_ctx = width * page
+        buffer = torch.tensor(plan.flat, dtype=torch.int32).to(device)
+        batch = batch_from_buffer(plan, buffer)
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # lazy initialisation (handles, attributes) must not be captured
+                self.model.forward(batch, self.cache)
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        before = native.LAUNCHES
+        with torch.cuda.graph(graph, pool=self.pool):
+            logits = self.model.forward(batch, self.cache)
+        if self.pool is None:
+            self.pool = graph.pool()
+        return _CapturedStep(graph, buffer, logits, native.LAUNCHES - before)
+
+    def run(self, entries) -> torch.Tensor:
+        """Replay the step for ``entries`` (one token each; pages already reserved).
+        Returns logits for the entries that want them, in entry order."""
+        bucket_entries = min(_bucket(len(entries)), _bucket(self.max_entries))
+        widest = max(
+            (len(self.cache.request(e.key).tables[g].pages) for e in entries for g in range(len(self.cache.groups))),
+            default=1,
+        )
+        key = (bucket_entries, _bucket(widest, 8))
+        # every entry is laid out as wanting its token, so that the layout is fixed
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        full = [type(e)(e.key, e.tokens, [0]) for e in entries]
+        step = self.captured.get(key)
+        if step is None:
+            step = self._capture(key)
+            self.captured[key] = step
+        plan = self._plan(full, *key)
+        assert len(plan.flat) == step.buffer.numel()
+        host = torch.tensor(plan.flat, dtype=torch.int32).pin_memory()
+        step.buffer.copy_(host, non_blocking=True)
+        step.graph.replay()
+        native.LAUNCHES += step.launches
+        if len(wanted) == len(entries):
+            return step.logits[: len(entries)]
+        if not wanted:
+            return step.logits[:0]
+        index = torch.tensor(wanted, dtype=torch.long, device=step.logits.device)
+        return step.logits.index_select(0, index)

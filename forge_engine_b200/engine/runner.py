@@ -20,6 +20,7 @@ from ..parts.base import BuildContext
 from ..weights.loader import load_checkpoint
 from ..weights.random_init import random_tensors
 from .batch import StepBatch, StepEntry, build_batch
+from .graphs import DecodeGraphs
 
 DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16,
           "fp32": torch.float32}
@@ -39,7 +40,8 @@ def resolve_dtype(name) -> torch.dtype:
 class ModelRunner:
     """Owns the model, the cache manager and the device status word."""
 
-    def __init__(self, model: DecoderModel, *, page_size: int, num_pages: int, max_requests: int) -> None:
+    def __init__(self, model: DecoderModel, *, page_size: int, num_pages: int, max_requests: int,
+                 use_graphs: bool = True) -> None:
         self.model = model
         self.ctx = model.ctx
         needs, shares = model.cache_needs()
@@ -54,11 +56,13 @@ class ModelRunner:
         )
         self.steps_run = 0
         self.tokens_run = 0
+        self.graphs = DecodeGraphs(model, self.cache, max_requests)
+        self.use_graphs = use_graphs and self.graphs.usable()
 
     # -- construction ------------------------------------------------------------------
     @classmethod
     def from_folder(cls, folder: str | Path, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
-                    num_pages: int = 1024, max_requests: int = 16) -> "ModelRunner":
+                    num_pages: int = 1024, max_requests: int = 16, use_graphs: bool = True) -> "ModelRunner":
         """Model class by config.json's architecture, weights by tensor name."""
         native.require_cuda()
         native.lib()
@@ -68,11 +72,12 @@ class ModelRunner:
         optional = (spec.head_name,) if spec.tie_embeddings else ()
         weights = load_checkpoint(folder, expected, engine_dtype, device, optional)
         return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
-                                num_pages=num_pages, max_requests=max_requests)
+                                num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs)
 
     @classmethod
     def from_random(cls, config: dict, seed: int, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
-                    num_pages: int = 1024, max_requests: int = 16, std: float = 0.02) -> "ModelRunner":
+                    num_pages: int = 1024, max_requests: int = 16, std: float = 0.02,
+                    use_graphs: bool = True) -> "ModelRunner":
         """Random weights drawn on the device (benchmark-sized models never touch the disk)."""
         native.require_cuda()
         native.lib()
@@ -80,18 +85,19 @@ class ModelRunner:
         _, _, spec = read_model_config(config)
         weights = random_tensors(expected_tensors(spec), seed, std=std, dtype=engine_dtype, device=device)
         return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
-                                num_pages=num_pages, max_requests=max_requests)
+                                num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs)
 
     @classmethod
     def from_tensors(cls, spec, weights: dict, *, dtype, device, page_size: int, num_pages: int,
-                     max_requests: int) -> "ModelRunner":
+                     max_requests: int, use_graphs: bool = True) -> "ModelRunner":
         native.require_cuda()
         native.lib()
         status = torch.zeros(1, dtype=torch.int32, device=device)
         ctx = BuildContext(dtype=resolve_dtype(dtype), device=torch.device(device), status=status)
         with torch.cuda.device(ctx.device):
             model = DecoderModel(spec, weights, ctx)
-            return cls(model, page_size=page_size, num_pages=num_pages, max_requests=max_requests)
+            return cls(model, page_size=page_size, num_pages=num_pages, max_requests=max_requests,
+                       use_graphs=use_graphs)
 
     # -- requests ------------------------------------------------------------------------
     def begin(self, key) -> None:
@@ -137,8 +143,13 @@ class ModelRunner:
             raise
         try:
             with torch.cuda.device(self.ctx.device):
-                batch = build_batch(entries, self.cache, self.ctx.device)
-                logits = self.model.forward(batch, self.cache)
+                if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+                    logits = self.graphs.run(entries)
+                    n_tokens = len(entries)
+                else:
+                    batch = build_batch(entries, self.cache, self.ctx.device)
+                    logits = self.model.forward(batch, self.cache)
+                    n_tokens = batch.n_tokens
         except BaseException:
             for key in reserved:
                 self.cache.trim(key, self.cache.request(key).length)
@@ -147,7 +158,7 @@ class ModelRunner:
             request = self.cache.request(entry.key)
             self.cache.advance(entry.key, request.length + len(entry.tokens))
         self.steps_run += 1
-        self.tokens_run += batch.n_tokens
+        self.tokens_run += n_tokens
         return logits
 
     def check_status(self) -> None:

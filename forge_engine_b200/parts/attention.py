@@ -21,9 +21,12 @@ from .linear import Linear, fuse_rows
 # The split decode kernel is launched with about this many blocks (4 per SM of a B200),
 # so that few requests with long contexts still fill the machine.
 SPLIT_TARGET_BLOCKS = 592
+MAX_SPLITS = 64   # what the merge kernel takes; every split gets at least two 64-key tiles
 
 
 class GQAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         if spec.head_dim % 16 or spec.head_dim > 256:
             raise UnsupportedShapeError(
@@ -110,7 +113,7 @@ class GQAttention(Mixer):
                 longest = min(longest, self.spec.window + limit)
             tiles = -(-longest // 64)
             blocks = len(small) * self.nkv
-            splits = max(1, min(tiles, -(-SPLIT_TARGET_BLOCKS // blocks)))
+            splits = max(1, min(-(-tiles // 2), MAX_SPLITS, -(-SPLIT_TARGET_BLOCKS // blocks)))
         native.attention_mma(
             qkv, qkv.shape[1], k_cache, v_cache, table, batch.cu_tokens, batch.starts,
             batch.n_entries, batch.max_new, self.spec.window, self.spec.scale, out, self.nq,

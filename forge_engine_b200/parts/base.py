@@ -94,6 +94,11 @@ class Mixer(Part):
     cache)`` gets the normalised activations [N, hidden] of all tokens of the step, the
     ``StepBatch`` and its ``CacheView``, and returns the update [N, hidden]."""
 
+    # True if ``forward`` only launches work on the current stream and decides nothing
+    # from device data or from the host copy of the entries beyond their counts, so that
+    # a decode step can be captured once in a CUDA graph and replayed.
+    graph_safe = False
+
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds()
 

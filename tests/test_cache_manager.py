@@ -152,7 +152,8 @@ def test_state_slots_are_zeroed_on_lease() -> None:
     b = cache.begin_request("b")
     assert b.slot == a.slot and float(state[b.slot].abs().sum()) == 0.0
     assert cache.view(0).state is state and cache.view(0).kv is None
-    assert cache.view(1).kv[0].shape == (4, 2, 4, 16)
+    # one page more than the pool leases: the null page of fixed-size batches
+    assert cache.view(1).kv[0].shape == (5, 2, 4, 16) and cache.null_page == 4
 
 
 @pytest.mark.parametrize("seed", range(6))

@@ -487,3 +487,51 @@ def test_toy_architecture_registers_builds_and_steps(fe, tmp_path) -> None:
     torch.testing.assert_close(torch.cat(rows_b), ref_b, atol=5e-5, rtol=1e-4)
     runner.end("a"), runner.end("b")
     runner.cache.check_consistency()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_equals_eager_steps(fe, dtype, tmp_path) -> None:
+    """Decode steps replayed from CUDA graphs (padded to bucket sizes, fixed table widths)
+    against the same steps launched eagerly, with requests joining and leaving."""
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+
+    cfg, weights = make_model_folder(tmp_path / "m", plain.TINY_C, 5)
+    ids = {k: random_ids(cfg.vocab_size, n, 30 + n) for k, n in (("a", 150), ("b", 40), ("c", 90))}
+    results = {}
+    for graphs in (False, True):
+        runner = ModelRunner.from_folder(tmp_path / "m", dtype=dtype, page_size=8, num_pages=64, max_requests=4,
+                                         use_graphs=graphs)
+        assert runner.use_graphs == graphs
+        rows = {k: [] for k in ids}
+        fed = {"a": 100, "b": 3, "c": 60}
+        for k in ids:
+            runner.begin(k)
+            runner.step([StepEntry(k, ids[k][: fed[k]], [])])
+        live = ["a", "b", "c"]
+        step = 0
+        while live:
+            entries = [StepEntry(k, [ids[k][fed[k]]], [0] if (step + i) % 3 else []) for i, k in enumerate(live)]
+            out = runner.step(entries).cpu()
+            row = 0
+            for e in entries:
+                if e.want:
+                    rows[e.key].append((fed[e.key], out[row].clone()))
+                    row += 1
+                fed[e.key] += 1
+            for k in [k for k in live if fed[k] == len(ids[k])]:
+                runner.end(k)
+                live.remove(k)
+            step += 1
+        runner.check_status()
+        assert runner.cache.leased_pages() == [0]
+        if graphs:
+            assert len(runner.graphs.captured) >= 2      # batches of 3 (bucket 4), 2 and 1
+        results[graphs] = rows
+    for k in ids:
+        ref = plain.forward_logits(ids[k], weights, cfg)
+        assert len(results[True][k]) == len(results[False][k]) > 10
+        for (pos_e, eager), (pos_g, replayed) in zip(results[False][k], results[True][k]):
+            assert pos_e == pos_g
+            torch.testing.assert_close(replayed, ref[pos_g], **bound(dtype, ref))
+            if dtype == "float32":
+                assert torch.equal(eager, replayed)
