@@ -1,0 +1,414 @@
+// y[n, o] = sum_k x[n, k] * w[o, k]  on the 5th-generation tensor cores (tcgen05), bfloat16
+// operands, 32-bit accumulators in tensor memory, operands staged by TMA.
+//
+// Orientation: the 128-row side of the MMA is the *weight* ([out, in] rows, K-major, as
+// nn.Linear stores them: src/forge_engine/qwen3.py:113-122), the N side is the tokens.
+// With few tokens (decode) a block still streams a full 128 x 64 weight tile per stage, so
+// the kernel is bound by reading the weights once; with many tokens N grows to 256.
+//
+//   block (6 warps):  warp 0  TMA producer: per 64-wide k-block one weight tile
+//                             [128 x 64] and one token tile [N x 64], 128-byte swizzle
+//                     warp 1  allocates tensor memory, issues tcgen05.mma (one lane),
+//                             commits to the stage's "empty" barrier
+//                     warps 2-5  epilogue: tcgen05.ld of their 32 accumulator lanes
+//                             (lane = output feature, column = token), bias / SiLU*mul /
+//                             residual add, coalesced stores along the feature dimension
+//   grid (feature tiles, token tiles, k-splits).  With k-splits > 1 every block writes its
+//   partial tile to a workspace; the block that arrives last adds them in split order and
+//   runs the epilogue, so results do not depend on timing.
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the block sets a bit in the
+// status word, stops issuing work, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;        // weight rows (output features) per block
+constexpr int BK = 64;         // k per stage: 128 bytes of bfloat16 = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr unsigned WAIT_LIMIT = 20000000u;
+
+enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3 };
+
+struct GemmParams {
+  void* y;
+  const float* bias;
+  int n, o, k;
+  int epilogue;
+  int ksplit;
+  float* ws_part;        // [feature tiles, token tiles, ksplit, BN, BM] floats
+  unsigned* ws_count;    // [feature tiles * token tiles], zero before and after a launch
+  int* status;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Non-blocking test of a phase, so that the loop around it has a bound of its own.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit was hit or another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag) {
+  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFFu) >> 4);   // start address
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset
+  d |= (uint64_t)1 << 46;                              // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                              // 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ unsigned umma_idesc(int n) {
+  unsigned d = 0;
+  d |= 1u << 4;                  // accumulator: f32
+  d |= 1u << 7;                  // A: bf16
+  d |= 1u << 10;                 // B: bf16
+  d |= (unsigned)(n >> 3) << 17; // N
+  d |= (unsigned)(BM >> 4) << 24;  // M
+  return d;                      // both operands K-major, no negation, dense
+}
+
+__device__ __forceinline__ void umma_f16(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc,
+                                         unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+
+template <int BN> __host__ __device__ constexpr int stages_for() {
+  // stage = weight tile (16 KB) + token tile (BN * 128 B); keep the ring under ~200 KB
+  return BN <= 32 ? 8 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
+}
+
+// Finished values of one accumulator row (feature) for 16 consecutive tokens.
+template <int EPI>
+__device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int feature, int token0, int lane) {
+  if (EPI == EPI_SILU_MUL_BF16) {
+    // weight rows alternate 16 gate features, 16 up features: lanes 0-15 hold gate,
+    // lanes 16-31 the matching up.  The lower half-warp finishes even tokens, the upper
+    // half odd ones, so both halves store.
+    const int half_o = p.o >> 1;
+    const int out_feature = (feature >> 5) * 16 + (lane & 15);
+    bf16* y = reinterpret_cast<bf16*>(p.y);
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      const float send = lane < 16 ? v[j + 1] : v[j];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
+      const int token = token0 + j + (lane < 16 ? 0 : 1);
+      const float r = lane < 16 ? silu_f(v[j]) * recv : silu_f(recv) * v[j + 1];
+      if (token < p.n && out_feature < half_o) y[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(r);
+    }
+    return;
+  }
+  if (feature >= p.o) return;
+  const float b = p.bias ? p.bias[feature] : 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int token = token0 + j;
+    if (token >= p.n) break;
+    const size_t at = (size_t)token * p.o + feature;
+    const float r = v[j] + b;
+    if (EPI == EPI_STORE_BF16) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(r);
+    else if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(p.y)[at] = r;
+    else reinterpret_cast<float*>(p.y)[at] += r;
+  }
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+  constexpr int STAGES = stages_for<BN>();
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment: the swizzle pattern repeats every 8 rows of 128 bytes
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* a_tiles = smem;
+  unsigned char* b_tiles = smem + STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + STAGES * B_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_done = empty + STAGES;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int kblocks = (p.k + BK - 1) / BK;
+  const int per_split = (kblocks + p.ksplit - 1) / p.ksplit;
+  const int kb_begin = blockIdx.z * per_split;
+  const int kb_end = min(kblocks, kb_begin + per_split);
+  const int my_blocks = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < my_blocks; ++i) {
+        const int s = i % STAGES;
+        const unsigned parity = ((i / STAGES) & 1) ^ 1;
+        if (!mbar_wait(empty + s, parity, abort_flag)) break;
+        mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+        const int kcoord = (kb_begin + i) * BK;
+        tma_load_2d(a_tiles + s * A_BYTES, &map_w, kcoord, m0, full + s);
+        tma_load_2d(b_tiles + s * B_BYTES, &map_x, kcoord, n0, full + s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const unsigned idesc = umma_idesc(BN);
+      bool ok = true;
+      for (int i = 0; i < my_blocks && ok; ++i) {
+        const int s = i % STAGES;
+        const unsigned parity = (i / STAGES) & 1;
+        ok = mbar_wait(full + s, parity, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t da = umma_desc(a_tiles + s * A_BYTES);
+        const uint64_t db = umma_desc(b_tiles + s * B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          // 16 k = 32 bytes further along the swizzled row: +2 in units of 16 bytes
+          umma_f16(tmem_base, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (i | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(empty + s);      // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(acc_done);         // arrives when every MMA issued above has finished
+    }
+  } else {
+    // epilogue warps 2..5 own accumulator lanes 32 * (warp % 4) .. +31
+    const int quarter = warp & 3;
+    const int feature = m0 + quarter * 32 + lane;
+    mbar_wait(acc_done, 0, abort_flag);
+    // all four epilogue warps take the same path: agree on the outcome of the wait
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = *abort_flag == 0;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
+    const bool split = p.ksplit > 1;
+    if (ok && !split) {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        if (my_blocks > 0) tmem_ld16(lane_base + c, v);
+        else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+        store16<EPI>(p, v, feature, n0 + c, lane);
+      }
+    } else if (ok) {
+      // publish the partial tile: ws[tile][split][token][feature]
+      const size_t tile = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+      float* mine = p.ws_part + (tile * p.ksplit + blockIdx.z) * (size_t)(BN * BM);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        if (my_blocks > 0) tmem_ld16(lane_base + c, v);
+        else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * BM + quarter * 32 + lane] = v[j];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const unsigned arrived = atomicAdd(p.ws_count + tile, 1u);
+        const int last = arrived == (unsigned)p.ksplit - 1u;
+        if (last) p.ws_count[tile] = 0u;
+        *last_flag = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        __threadfence();
+        const float* all = p.ws_part + tile * p.ksplit * (size_t)(BN * BM);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int sp = 0; sp < p.ksplit; ++sp) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              v[j] += __ldcg(all + (size_t)sp * (BN * BM) + (size_t)(c + j) * BM + quarter * 32 + lane);
+          }
+          store16<EPI>(p, v, feature, n0 + c, lane);
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, FE_STATUS_WAIT_TIMEOUT);
+}
+
+template <int BN> constexpr size_t smem_bytes() {
+  return (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + (2 * stages_for<BN>() + 1) * 8 + 16 + 1024;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [rows, k] bfloat16, row-major; box = box_rows x 64 elements, 128-byte swizzle; reads
+// outside the tensor give zeros.
+int make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return FE_ERR_BAD_SHAPE;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
+}
+
+template <int BN, int EPI>
+int launch_one(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem_bytes<BN>());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  gemm_tc5_kernel<BN, EPI><<<grid, THREADS, smem_bytes<BN>(), stream>>>(mw, mx, p);
+  return fe_last_error();
+}
+
+template <int BN>
+int launch_bn(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  switch (p.epilogue) {
+    case EPI_STORE_BF16: return launch_one<BN, EPI_STORE_BF16>(mw, mx, p, grid, stream);
+    case EPI_STORE_F32: return launch_one<BN, EPI_STORE_F32>(mw, mx, p, grid, stream);
+    case EPI_ADD_F32: return launch_one<BN, EPI_ADD_F32>(mw, mx, p, grid, stream);
+    case EPI_SILU_MUL_BF16: return launch_one<BN, EPI_SILU_MUL_BF16>(mw, mx, p, grid, stream);
+  }
+  return FE_ERR_BAD_DTYPE;
+}
+
+}  // namespace
+
+// Token-tile width the kernel uses for n tokens.
+FE_EXPORT int fe_gemm_tc5_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256))); }
+
+// epilogue: 0 store bf16 [n, o]; 1 store f32 [n, o]; 2 add into f32 [n, o];
+// 3 y[n, o/2] = silu(gate) * up (bf16) for w whose rows alternate 16 gate, 16 up features.
+// ksplit > 1 needs ws_part (floats: feature tiles * token tiles * ksplit * tile * 128) and
+// ws_count (one zeroed unsigned per output tile; left zeroed).
+FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
+                          int epilogue, int ksplit, float* ws_part, unsigned* ws_count, int* status,
+                          cudaStream_t stream) {
+  if (n <= 0 || o <= 0) return 0;
+  if (k <= 0 || (k % 8) != 0) return FE_ERR_BAD_SHAPE;
+  if (epilogue == EPI_SILU_MUL_BF16 && ((o % 32) != 0 || bias != nullptr)) return FE_ERR_BAD_SHAPE;
+  if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return FE_ERR_BAD_ALIGN;
+  if (ksplit < 1) ksplit = 1;
+  const int kblocks = (k + BK - 1) / BK;
+  if (ksplit > kblocks) ksplit = kblocks;
+  if (ksplit > 1 && (ws_part == nullptr || ws_count == nullptr)) return FE_ERR_BAD_SHAPE;
+  const int bn = fe_gemm_tc5_tile(n);
+  CUtensorMap mw, mx;
+  int rc = make_map(&mw, w, o, k, BM);
+  if (rc) return rc;
+  rc = make_map(&mx, x, n, k, bn);
+  if (rc) return rc;
+  GemmParams p{y, bias, n, o, k, epilogue, ksplit, ws_part, ws_count, status};
+  dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
+  if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;
+  switch (bn) {
+    case 16: return launch_bn<16>(mw, mx, p, grid, stream);
+    case 32: return launch_bn<32>(mw, mx, p, grid, stream);
+    case 64: return launch_bn<64>(mw, mx, p, grid, stream);
+    case 128: return launch_bn<128>(mw, mx, p, grid, stream);
+    default: return launch_bn<256>(mw, mx, p, grid, stream);
+  }
+}

@@ -62,6 +62,8 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_attention_simt": [p, i, i, p, p, p, i, i, i, p, p, i, f, p, i, i, i, i, p, p],
         "fe_gemm_simt": [p, i, p, i, p, p, i, i, i, i, i, p],
         "fe_sample": [p, i, i, p, p, p, p, p, p, p, p, p],
+        "fe_gemm_skinny": [p, p, p, p, i, i, i, i, i, p, p, p],
+        "fe_gemm_tc5": [p, p, p, p, i, i, i, i, i, p, p, p, p],
     }
     for name, argtypes in signatures.items():
         fn = getattr(handle, name)
@@ -322,6 +324,107 @@ def gemm_simt(
                            1 if accumulate else 0, stream()),
         "gemm_simt",
     )
+
+
+SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ADD_F32, SKINNY_SILU_MUL = 0, 1, 2, 3
+SKINNY_MAX_ROWS = 64
+
+
+_skinny_scratch: dict = {}
+
+
+def _skinny_workspace(device, tiles: int, ksplit: int):
+    """Partial-tile buffer and arrival counters for split-k launches on ``device``.  The
+    counters are zeroed once; every launch leaves them zeroed again."""
+    entry = _skinny_scratch.get(device)
+    need_part, need_count = tiles * ksplit * 16 * 64, tiles
+    if entry is None or entry[0].numel() < need_part or entry[1].numel() < need_count:
+        part = torch.empty(max(need_part, 1 << 20), dtype=torch.float32, device=device)
+        count = torch.zeros(max(need_count, 16384), dtype=torch.int32, device=device)
+        entry = (part, count)
+        _skinny_scratch[device] = entry
+    return entry
+
+
+def skinny_ksplit(o: int, k: int) -> int:
+    """Blocks per 16-feature tile so that a small matrix still fills the machine."""
+    tiles = -(-o // 16)
+    if tiles >= 592:
+        return 1
+    return max(1, min(8, 592 // tiles, k // 2048 if k >= 4096 else k // 1024))
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
+                bias: torch.Tensor | None = None, ksplit: int | None = None) -> None:
+    """out = x @ w.T for at most 64 rows of x (bfloat16 operands, weights streamed once).
+
+    epilogue 0: out bf16 [n, o]; 1: out f32 [n, o]; 2: out f32 [n, o] += product;
+    3: out bf16 [n, o/2] = silu(gate) * up for w whose rows alternate 8 gate, 8 up features."""
+    _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
+    n, k = x.shape
+    o = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
+    if epilogue == SKINNY_SILU_MUL:
+        assert out.shape == (n, o // 2) and out.dtype == torch.bfloat16
+    else:
+        assert out.shape == (n, o)
+        assert out.dtype == (torch.bfloat16 if epilogue == SKINNY_STORE_BF16 else torch.float32)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == o)
+    if ksplit is None:
+        ksplit = skinny_ksplit(o, k)
+    part = count = None
+    if ksplit > 1:
+        part, count = _skinny_workspace(x.device, -(-o // 16), ksplit)
+    check(lib().fe_gemm_skinny(ptr(x), ptr(w), ptr(bias), ptr(out), n, o, k, int(epilogue), int(ksplit),
+                               ptr(part), ptr(count), stream()),
+          "gemm_skinny")
+
+
+TC5_STORE_BF16, TC5_STORE_F32, TC5_ADD_F32, TC5_SILU_MUL = 0, 1, 2, 3
+_tc5_scratch: dict = {}
+
+
+def tc5_tile(n: int) -> int:
+    return 16 if n <= 16 else 32 if n <= 32 else 64 if n <= 64 else 128 if n <= 128 else 256
+
+
+def _tc5_workspace(device, tiles: int, ksplit: int, tile_n: int):
+    entry = _tc5_scratch.get(device)
+    need_part, need_count = tiles * ksplit * tile_n * 128, tiles
+    if entry is None or entry[0].numel() < need_part or entry[1].numel() < need_count:
+        part = torch.empty(max(need_part, 1 << 22), dtype=torch.float32, device=device)
+        count = torch.zeros(max(need_count, 16384), dtype=torch.int32, device=device)
+        entry = (part, count)
+        _tc5_scratch[device] = entry
+    return entry
+
+
+def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: torch.Tensor,
+             bias: torch.Tensor | None = None, ksplit: int = 1) -> None:
+    """out = x @ w.T on tcgen05 tensor cores (bfloat16 operands, TMA-fed).
+
+    epilogue 0: out bf16 [n, o]; 1: out f32 [n, o]; 2: out f32 [n, o] += product;
+    3: out bf16 [n, o/2] = silu(gate) * up for w whose rows alternate 16 gate, 16 up features.
+    ``ksplit`` blocks share an output tile (deterministic reduction through a workspace)."""
+    _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
+    n, k = x.shape
+    o = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
+    if epilogue == TC5_SILU_MUL:
+        assert out.shape == (n, o // 2) and out.dtype == torch.bfloat16
+    else:
+        assert out.shape == (n, o)
+        assert out.dtype == (torch.bfloat16 if epilogue == TC5_STORE_BF16 else torch.float32)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == o)
+    part = count = None
+    ksplit = max(1, min(int(ksplit), -(-k // 64)))
+    if ksplit > 1:
+        tile_n = tc5_tile(n)
+        tiles = -(-o // 128) * -(-n // tile_n)
+        part, count = _tc5_workspace(x.device, tiles, ksplit, tile_n)
+    check(lib().fe_gemm_tc5(ptr(x), ptr(w), ptr(bias), ptr(out), n, o, k, int(epilogue), ksplit, ptr(part),
+                            ptr(count), ptr(status), stream()),
+          "gemm_tc5")
 
 
 def sample(
