@@ -126,46 +126,57 @@ FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dty
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
-  const int row = blockIdx.x;
-  const T* g = gate_up + (size_t)row * 2 * inter;
-  const T* u = g + inter;
-  T* o = out + (size_t)row * inter;
-  const int i = blockIdx.y * blockDim.x + threadIdx.x;
-  if (i < inter) o[i] = from_float<T>(silu(to_float(g[i])) * to_float(u[i]));
+// block == 0: a row is [all gate | all up]; block == B > 0: a row alternates B gate
+// features, B up features (the layout the fused projection kernels want).
+__device__ __forceinline__ void silu_sources(int i, int inter, int block, int* gate_at, int* up_at) {
+  if (block == 0) { *gate_at = i; *up_at = inter + i; }
+  else { const int b = i / block; *gate_at = 2 * b * block + (i - b * block); *up_at = *gate_at + block; }
 }
 
 template <typename T>
-__global__ void silu_mul_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block) {
   const int row = blockIdx.x;
   const T* g = gate_up + (size_t)row * 2 * inter;
-  const T* u = g + inter;
+  T* o = out + (size_t)row * inter;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= inter) return;
+  int ga, ua;
+  silu_sources(i, inter, block, &ga, &ua);
+  o[i] = from_float<T>(silu(to_float(g[ga])) * to_float(g[ua]));
+}
+
+template <typename T>
+__global__ void silu_mul_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block) {
+  const int row = blockIdx.x;
+  const T* g = gate_up + (size_t)row * 2 * inter;
   T* o = out + (size_t)row * inter;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (i >= inter) return;
+  int ga, ua;
+  silu_sources(i, inter, block, &ga, &ua);   // block is a multiple of 8, so 8 features stay together
   float a[8], b[8];
-  load8(g + i, a);
-  load8(u + i, b);
+  load8(g + ga, a);
+  load8(g + ua, b);
 #pragma unroll
   for (int k = 0; k < 8; ++k) a[k] = silu(a[k]) * b[k];
   store8(o + i, a);
 }
 
-FE_EXPORT int fe_silu_mul(const void* gate_up, void* out, int dtype, int rows, int inter,
+FE_EXPORT int fe_silu_mul(const void* gate_up, void* out, int dtype, int rows, int inter, int block,
                           cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const bool vec = (inter % 8) == 0 && ((uintptr_t)gate_up % 32) == 0 && ((uintptr_t)out % 32) == 0;
+  if (block < 0 || (block > 0 && (inter % block) != 0)) return FE_ERR_BAD_SHAPE;
+  const bool vec = (inter % 8) == 0 && (block % 8) == 0 && ((uintptr_t)gate_up % 32) == 0 && ((uintptr_t)out % 32) == 0;
   const int threads = 256;
   const int per = vec ? 8 : 1;
   dim3 grid(rows, (inter + threads * per - 1) / (threads * per));
   if (grid.y > 65535) return FE_ERR_TOO_LARGE;
   if (dtype == FE_DTYPE_F32) {
-    if (vec) silu_mul_vec8_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter);
-    else silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+    if (vec) silu_mul_vec8_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, block);
+    else silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, block);
   } else if (dtype == FE_DTYPE_BF16) {
-    if (vec) silu_mul_vec8_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
-    else silu_mul_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter);
+    if (vec) silu_mul_vec8_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, block);
+    else silu_mul_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, block);
   } else {
     return FE_ERR_BAD_DTYPE;
   }

@@ -127,8 +127,10 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 
 template <int BN> __host__ __device__ constexpr int stages_for() {
-  // stage = weight tile (16 KB) + token tile (BN * 128 B); keep the ring under ~200 KB
-  return BN <= 32 ? 8 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
+  // stage = weight tile (16 KB) + token tile (BN * 128 B).  Narrow token tiles keep the ring
+  // small enough for three (BN <= 16) or two blocks per SM, so that one block's epilogue and
+  // set-up overlap another's streaming; the widest tile takes the SM alone.
+  return BN <= 128 ? (BN == 128 ? 3 : 4) : 4;
 }
 
 // Finished values of one accumulator row (feature) for 16 consecutive tokens.
@@ -166,7 +168,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
 }
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
   constexpr int STAGES = stages_for<BN>();
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;

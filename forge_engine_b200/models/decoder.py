@@ -55,7 +55,7 @@ class DecoderModel:
             {local: weights[f"{spec.final_norm_name}.{local}"] for local in norm_shapes},
             ctx,
         )
-        self.head = Linear(self.embed if spec.tie_embeddings else weights[spec.head_name])
+        self.head = Linear(self.embed if spec.tie_embeddings else weights[spec.head_name], status=ctx.status)
         for index, run in enumerate(spec.schedule):
             if not 0 <= run.layer < len(self.blocks):
                 raise ValueError(f"run {index} names layer {run.layer}, which does not exist")

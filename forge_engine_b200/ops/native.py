@@ -57,7 +57,7 @@ def _declare(handle: ctypes.CDLL) -> None:
     signatures = {
         "fe_embedding": [p, p, i, p, i, i, i, p, p],
         "fe_add_rmsnorm": [p, p, i, p, p, i, p, i, i, f, i, p],
-        "fe_silu_mul": [p, p, i, i, i, p],
+        "fe_silu_mul": [p, p, i, i, i, i, p],
         "fe_qk_rope_cache": [p, i, p, p, f, p, i, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
         "fe_attention_simt": [p, i, i, p, p, p, i, i, i, p, p, i, f, p, i, i, i, i, p, p],
         "fe_gemm_simt": [p, i, p, i, p, p, i, i, i, i, i, p],
@@ -185,12 +185,13 @@ def add_rmsnorm(
     )
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out[n, i] = silu(gate[n, i]) * up[n, i].  ``block`` 0: a row of ``gate_up`` is all gate
+    features then all up features; ``block`` B: it alternates B gate, B up features."""
     _dense(gate_up, "gate_up"), _dense(out, "out")
     rows, inter = out.shape
     assert gate_up.shape == (rows, 2 * inter) and gate_up.dtype == out.dtype
-    check(lib().fe_silu_mul(ptr(gate_up), ptr(out), code(out), rows, inter, stream()), "silu_mul")
+    check(lib().fe_silu_mul(ptr(gate_up), ptr(out), code(out), rows, inter, int(block), stream()), "silu_mul")
 
 
 def qk_rope_cache(
@@ -397,6 +398,16 @@ def _tc5_workspace(device, tiles: int, ksplit: int, tile_n: int):
         entry = (part, count)
         _tc5_scratch[device] = entry
     return entry
+
+
+TC5_MAX_ROWS = 64   # up to this many rows the tcgen05 kernel is used instead of the library GEMM
+
+
+def tc5_ksplit(o: int, k: int) -> int:
+    """Blocks per output tile: enough blocks to cover the SMs when the weight has few
+    128-row tiles, never so many that a block gets less than eight 64-wide k-blocks."""
+    tiles = -(-o // 128)
+    return max(1, min(-(-148 // tiles), 4, (k // 64) // 8))
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: torch.Tensor,

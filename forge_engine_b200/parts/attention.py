@@ -43,8 +43,10 @@ class GQAttention(Mixer):
         self.qkv_proj = Linear(
             fuse_rows([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]]),
             bias,
+            status=ctx.status,
         )
-        self.o_proj = Linear(weights["o_proj.weight"], weights.get("o_proj.bias") if spec.bias else None)
+        self.o_proj = Linear(weights["o_proj.weight"], weights.get("o_proj.bias") if spec.bias else None,
+                             status=ctx.status)
         self.q_norm = self.k_norm = None
         if spec.qk_norm:
             self.q_norm = weights["q_norm.weight"].float().contiguous()

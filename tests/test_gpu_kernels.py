@@ -88,6 +88,12 @@ def test_silu_mul(native, dtype, inter) -> None:
     xd = x.double()
     ref = torch.nn.functional.silu(xd[:, :inter]) * xd[:, inter:]
     torch.testing.assert_close(out.double(), ref, **tol(dtype))
+    for block in (8, 16) if inter % 16 == 0 else ():
+        # rows that alternate `block` gate and `block` up features
+        blocks = xd.view(19, inter // block, 2, block)
+        ref = (torch.nn.functional.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(19, inter)
+        native.silu_mul(x, out, block)
+        torch.testing.assert_close(out.double(), ref, **tol(dtype))
 
 
 @pytest.mark.parametrize("xd,wd,yd", [
@@ -390,3 +396,61 @@ def test_sampling_rows_are_independent(native) -> None:
         t, k, p, m = params[r]
         want, _, _ = twin_draw(logits[r], t, k or None, p, m, r + 1, [0, 5, 9, 2][r])
         assert got[r] == want
+
+
+# ---------------------------------------------------------------------------
+# tensor-core products for few rows
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n,o,k,ksplit", [(1, 256, 128, 1), (8, 331, 72, 1), (5, 384, 200, 2), (33, 640, 2560, 4),
+                                            (64, 2560, 4096, 8), (100, 331, 72, 1), (300, 1000, 512, 2)])
+def test_gemm_tc5(native, n, o, k, ksplit) -> None:
+    g = torch.Generator().manual_seed(n + o)
+    x = torch.randn((n, k), generator=g).bfloat16().to(DEV)
+    w = (torch.randn((o, k), generator=g) * 0.1).bfloat16().to(DEV)
+    bias = torch.randn(o, generator=g).to(DEV)
+    ref = x.double() @ w.double().t()
+    status = status_word()
+    out = torch.full((n, o), float("nan"), dtype=torch.float32, device=DEV)
+    native.gemm_tc5(x, w, out, native.TC5_STORE_F32, status, ksplit=ksplit)
+    torch.testing.assert_close(out.double(), ref, atol=2e-4, rtol=1e-5)
+    out16 = torch.empty((n, o), dtype=torch.bfloat16, device=DEV)
+    native.gemm_tc5(x, w, out16, native.TC5_STORE_BF16, status, bias=bias, ksplit=ksplit)
+    torch.testing.assert_close(out16.double(), ref + bias.double(), atol=3e-2, rtol=1e-2)
+    base = torch.randn((n, o), generator=g).to(DEV)
+    acc = base.clone()
+    native.gemm_tc5(x, w, acc, native.TC5_ADD_F32, status, ksplit=ksplit)
+    torch.testing.assert_close(acc.double(), ref + base.double(), atol=2e-4, rtol=1e-5)
+    # a second launch finds the arrival counters zeroed again
+    native.gemm_tc5(x, w, out, native.TC5_STORE_F32, status, ksplit=ksplit)
+    torch.testing.assert_close(out.double(), ref, atol=2e-4, rtol=1e-5)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("n,inter,k,ksplit", [(3, 64, 96, 1), (24, 256, 256, 2), (64, 9728, 2560, 1)])
+def test_gemm_tc5_silu_mul(native, n, inter, k, ksplit) -> None:
+    from forge_engine_b200.parts.linear import interleave_rows
+
+    g = torch.Generator().manual_seed(inter)
+    x = torch.randn((n, k), generator=g).bfloat16().to(DEV)
+    gate = (torch.randn((inter, k), generator=g) * 0.05).bfloat16().to(DEV)
+    up = (torch.randn((inter, k), generator=g) * 0.05).bfloat16().to(DEV)
+    w = interleave_rows(gate, up, 16)
+    ref = torch.nn.functional.silu(x.double() @ gate.double().t()) * (x.double() @ up.double().t())
+    out = torch.empty((n, inter), dtype=torch.bfloat16, device=DEV)
+    status = status_word()
+    native.gemm_tc5(x, w, out, native.TC5_SILU_MUL, status, ksplit=ksplit)
+    torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=1e-2)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("n,o,k", [(1, 331, 80), (8, 6144, 2560), (16, 400, 200), (40, 203, 136), (64, 2560, 4096)])
+def test_gemm_skinny(native, n, o, k) -> None:
+    g = torch.Generator().manual_seed(n + o)
+    x = torch.randn((n, k), generator=g).bfloat16().to(DEV)
+    w = (torch.randn((o, k), generator=g) * 0.1).bfloat16().to(DEV)
+    ref = x.double() @ w.double().t()
+    for ksplit in (1, 3):
+        out = torch.full((n, o), float("nan"), dtype=torch.float32, device=DEV)
+        native.gemm_skinny(x, w, out, native.SKINNY_STORE_F32, ksplit=ksplit)
+        torch.testing.assert_close(out.double(), ref, atol=2e-4, rtol=1e-5)
