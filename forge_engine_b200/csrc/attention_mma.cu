@@ -60,6 +60,7 @@ struct AttnParams {
   int num_splits;
   float* ws_acc;         // [entries, nkv, splits, 16, D]
   float* ws_ml;          // [entries, nkv, splits, 16, 2]
+  unsigned* ws_count;    // [entries, nkv] zeroed arrival counters, or null: a merge kernel follows
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) {
@@ -244,6 +245,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   bf16* kbuf = qs + BM * LD;                      // [2][BN][LD]
   bf16* vbuf = kbuf + 2 * BN * LD;                // [2][BN][LD]
 
+  pdl_trigger();
+  pdl_wait();
   const int entry = blockIdx.y, kvh = blockIdx.z;
   const int tok0 = p.cu_tokens[entry];
   const int n_new = p.cu_tokens[entry + 1] - tok0;
@@ -324,12 +327,18 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   }
 }
 
+constexpr int DEC_STAGES = 3;       // key/value tiles in flight per block (ring)
+constexpr int MERGE_MAX_SPLITS = 64;
+
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [16][LD]
-  bf16* kbuf = qs + DEC_ROWS * LD;                // [2][BN][LD]
-  bf16* vbuf = kbuf + 2 * BN * LD;                // [2][BN][LD]
+  bf16* kbuf = qs + DEC_ROWS * LD;                // [DEC_STAGES][BN][LD]
+  bf16* vbuf = kbuf + DEC_STAGES * BN * LD;       // [DEC_STAGES][BN][LD]
+  __shared__ int last_block;
 
+  pdl_trigger();
+  pdl_wait();
   const int split = blockIdx.x, entry = blockIdx.y, kvh = blockIdx.z;
   const int tok0 = p.cu_tokens[entry];
   const int n_new = p.cu_tokens[entry + 1] - tok0;
@@ -347,6 +356,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
   const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
   const int tile_begin = tile_first + split * per_split;
   const int tile_end = min(tile_stop, tile_begin + per_split);
+  const int my_tiles = max(0, tile_end - tile_begin);
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[D / 8][4];
@@ -357,33 +367,39 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
   const int pos_a = ra < rows_total ? start + ra / p.groups : -1;
   const int pos_b = rb < rows_total ? start + rb / p.groups : -1;
 
-  if (tile_begin < tile_end) {
+  if (my_tiles > 0) {
+    // ring of DEC_STAGES tiles: tiles i+1 .. i+DEC_STAGES-1 are in flight while tile i is used
     load_q_rows(qs, p, tok0, kvh, 0, rows_total, DEC_ROWS, tid, THREADS);
-    load_kv_tile(kbuf, vbuf, p, table, kvh, tile_begin * BN, key_lo, key_end, tid);
-    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i) {
+      if (i < my_tiles)
+        load_kv_tile(kbuf + i * BN * LD, vbuf + i * BN * LD, p, table, kvh, (tile_begin + i) * BN, key_lo, key_end, tid);
+      cp_async_commit();
+    }
     unsigned qf[D / 16][4];
-    for (int tile = tile_begin; tile < tile_end; ++tile) {
-      const int buf = (tile - tile_begin) & 1;
-      if (tile + 1 < tile_end) {
-        load_kv_tile(kbuf + (buf ^ 1) * BN * LD, vbuf + (buf ^ 1) * BN * LD, p, table, kvh, (tile + 1) * BN,
-                     key_lo, key_end, tid);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
+    for (int i = 0; i < my_tiles; ++i) {
+      const int ahead = i + DEC_STAGES - 1;
+      if (ahead < my_tiles) {
+        const int sa = ahead % DEC_STAGES;
+        load_kv_tile(kbuf + sa * BN * LD, vbuf + sa * BN * LD, p, table, kvh, (tile_begin + ahead) * BN, key_lo,
+                     key_end, tid);
       }
+      cp_async_commit();
+      cp_async_wait<DEC_STAGES - 1>();
       __syncthreads();
-      if (tile == tile_begin) {
+      if (i == 0) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           ldmatrix_x4(qf[kk], qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
       }
-      const int key0 = tile * BN + warp * 16;   // this warp's 16 keys of the tile
+      const int stage = i % DEC_STAGES;
+      const int key0 = (tile_begin + i) * BN + warp * 16;   // this warp's 16 keys of the tile
       if (key0 < key_end)
-        tile_step<16>(qf, kbuf + buf * BN * LD, vbuf + buf * BN * LD, warp * 16, key0, key_end, pos_a, pos_b,
+        tile_step<16>(qf, kbuf + stage * BN * LD, vbuf + stage * BN * LD, warp * 16, key0, key_end, pos_a, pos_b,
                       p.window, p.scale_log2, true, m, l, o, lane);
       __syncthreads();
     }
+    cp_async_wait<0>();
   }
 
   // merge the four warps: reuse the (now idle) key/value buffers
@@ -406,6 +422,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
   }
   __syncthreads();
   const int num_q_heads = p.nkv * p.groups;
+  const size_t pair = (size_t)entry * p.nkv + kvh;
   for (int idx = tid; idx < rows_total * D; idx += THREADS) {
     const int row = idx / D, d = idx - row * D;
     float big = -INFINITY;
@@ -424,7 +441,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
       p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
           __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     } else {
-      const size_t slot = ((size_t)entry * p.nkv + kvh) * p.num_splits + split;
+      const size_t slot = pair * p.num_splits + split;
       p.ws_acc[(slot * DEC_ROWS + row) * D + d] = num;
       if (d == 0) {
         p.ws_ml[(slot * DEC_ROWS + row) * 2] = big;
@@ -432,15 +449,70 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
       }
     }
   }
+  if (p.num_splits == 1 || p.ws_count == nullptr) return;   // one split, or a separate merge kernel follows
+
+  // The block that publishes its partial result last combines all of them, in split
+  // order, so that no second kernel is needed and the sum does not depend on timing.
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned arrived = atomicAdd(p.ws_count + pair, 1u);
+    last_block = arrived == (unsigned)p.num_splits - 1u;
+    if (last_block) p.ws_count[pair] = 0u;
+  }
+  __syncthreads();
+  if (!last_block) return;
+  __threadfence();
+  float* weight_s = reinterpret_cast<float*>(kbuf);       // [16][MERGE_MAX_SPLITS]
+  const int splits = p.num_splits;
+  const size_t slot0 = pair * splits;
+  for (int row = warp; row < rows_total; row += THREADS / 32) {
+    float mv[MERGE_MAX_SPLITS / 32], lv[MERGE_MAX_SPLITS / 32];
+    float big = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int sp = lane + i * 32;
+      mv[i] = -INFINITY; lv[i] = 0.f;
+      if (sp < splits) {
+        mv[i] = __ldcg(p.ws_ml + ((slot0 + sp) * DEC_ROWS + row) * 2);
+        lv[i] = __ldcg(p.ws_ml + ((slot0 + sp) * DEC_ROWS + row) * 2 + 1);
+      }
+      big = fmaxf(big, mv[i]);
+    }
+    big = warp_max(big);
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      mv[i] = (mv[i] == -INFINITY) ? 0.f : exp2f(mv[i] - big);
+      den += lv[i] * mv[i];
+    }
+    den = warp_sum(den);
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int sp = lane + i * 32;
+      if (sp < splits) weight_s[row * MERGE_MAX_SPLITS + sp] = mv[i] * inv;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows_total * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    const float* src = p.ws_acc + (slot0 * DEC_ROWS + row) * D + d;
+    float num = 0.f;
+#pragma unroll 4
+    for (int sp = 0; sp < splits; ++sp) num += __ldcg(src + (size_t)sp * DEC_ROWS * D) * weight_s[row * MERGE_MAX_SPLITS + sp];
+    const int token = row / p.groups, g = row - token * p.groups;
+    p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] = __float2bfloat16_rn(num);
+  }
 }
 
 // Combine the splits' (max, sum, acc) of every row: block = (entry, kv head).  The splits'
 // weights exp2(m_s - max) / sum are worked out once per row in shared memory; then every
 // thread owns one or more columns and sums over the splits with independent loads.
-constexpr int MERGE_MAX_SPLITS = 64;
-
 __global__ void __launch_bounds__(THREADS) attn_merge_kernel(AttnParams p) {
   __shared__ float weight_s[DEC_ROWS][MERGE_MAX_SPLITS];
+  pdl_trigger();
+  pdl_wait();
   const int entry = blockIdx.x, kvh = blockIdx.y;
   const int tok0 = p.cu_tokens[entry];
   const int n_new = p.cu_tokens[entry + 1] - tok0;
@@ -491,9 +563,10 @@ __global__ void __launch_bounds__(THREADS) attn_merge_kernel(AttnParams p) {
 }
 
 constexpr size_t PREFILL_SMEM = (size_t)(BM + 4 * BN) * LD * sizeof(bf16);
-constexpr size_t DECODE_KV_SMEM = (size_t)(DEC_ROWS + 4 * BN) * LD * sizeof(bf16);
+constexpr size_t DECODE_KV_SMEM = (size_t)(DEC_ROWS + 2 * DEC_STAGES * BN) * LD * sizeof(bf16);
 constexpr size_t DECODE_MERGE_SMEM =
-    (size_t)DEC_ROWS * LD * sizeof(bf16) + (size_t)4 * DEC_ROWS * (D + 2) * sizeof(float);
+    (size_t)DEC_ROWS * LD * sizeof(bf16) + (size_t)4 * DEC_ROWS * (D + 2) * sizeof(float) +
+    (size_t)DEC_ROWS * MERGE_MAX_SPLITS * sizeof(float);
 constexpr size_t DECODE_SMEM = DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM;
 
 }  // namespace
@@ -503,6 +576,8 @@ FE_EXPORT long long SYM(fe_attn_workspace_floats_d)(int entries, int num_kv_head
   return (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
 }
 
+// `counters` (one zeroed unsigned per entry and kv head, left zeroed) lets the decode
+// kernel combine its splits itself; without it a merge kernel is launched.
 // mode bit 0: run the prefill kernel for entries with more than `decode_rows` rows;
 // mode bit 1: run the decode kernel (and the merge, if num_splits > 1) for the others.
 // decode_rows is 16 when the decode kernel may be used, 0 to send everything to prefill.
@@ -511,7 +586,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
                                       int page_size, int num_pages, int num_kv_heads, int groups,
                                       const int* cu_tokens, const int* starts, int entries, int max_new,
                                       int window, float scale, int mode, int num_splits, float* workspace,
-                                      int* status, cudaStream_t stream) {
+                                      unsigned* counters, int* status, cudaStream_t stream) {
   if (entries <= 0) return 0;
   if (groups < 1 || groups > DEC_ROWS || num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return FE_ERR_BAD_SHAPE;
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
@@ -526,6 +601,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
   p.num_splits = num_splits;
   p.ws_acc = workspace;
   p.ws_ml = workspace ? workspace + (size_t)entries * num_kv_heads * num_splits * DEC_ROWS * D : nullptr;
+  p.ws_count = counters;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -542,17 +618,20 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
     if (max_rows > decode_rows) {
       p.row_lo = decode_rows; p.row_hi = 0x7fffffff;
       dim3 grid((max_rows + BM - 1) / BM, entries, num_kv_heads);
-      attn_prefill_kernel<<<grid, THREADS, PREFILL_SMEM, stream>>>(p);
+      const int rc = fe_launch_dependent(attn_prefill_kernel, grid, dim3(THREADS), PREFILL_SMEM, stream, p);
+      if (rc) return rc;
     }
   }
   if (use_decode) {
     if (num_splits > 1 && workspace == nullptr) return FE_ERR_BAD_SHAPE;
     p.row_lo = 0; p.row_hi = DEC_ROWS;
     dim3 grid(num_splits, entries, num_kv_heads);
-    attn_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(p);
-    if (num_splits > 1) {
+    int rc = fe_launch_dependent(attn_decode_kernel, grid, dim3(THREADS), DECODE_SMEM, stream, p);
+    if (rc) return rc;
+    if (num_splits > 1 && counters == nullptr) {
       dim3 mgrid(entries, num_kv_heads);
-      attn_merge_kernel<<<mgrid, THREADS, 0, stream>>>(p);
+      rc = fe_launch_dependent(attn_merge_kernel, mgrid, dim3(THREADS), 0, stream, p);
+      if (rc) return rc;
     }
   }
   return fe_last_error();
@@ -617,6 +696,7 @@ FE_EXPORT int SYM(fe_attention_decode_noalloc_d)(const void* q, int q_stride, vo
   p.num_splits = num_splits;
   p.ws_acc = scratch;
   p.ws_ml = scratch + (size_t)entries * num_kv_heads * num_splits * DEC_ROWS * D;
+  p.ws_count = nullptr;
   p.row_lo = 0; p.row_hi = DEC_ROWS;
   dim3 grid(num_splits, entries, num_kv_heads);
   attn_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(p);

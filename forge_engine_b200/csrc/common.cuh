@@ -9,6 +9,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+
+#include <utility>
 
 #define FE_DTYPE_F32 0
 #define FE_DTYPE_BF16 1
@@ -95,3 +98,39 @@ __device__ __forceinline__ void store8(bf16* p, const float* v) {
 }
 
 static inline int fe_last_error() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  A kernel that is launched "dependent" may start while
+// the kernel before it on the stream is still running; it must execute pdl_wait() before it
+// reads or writes anything that kernel (or an earlier one) touches.  pdl_trigger() in a
+// kernel lets the next kernel, if it was launched dependent, start early.  Both are no-ops
+// for kernels launched the ordinary way.
+// FORGE_ENGINE_PDL=0 in the environment launches every kernel the ordinary way.
+static inline int fe_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* text = getenv("FORGE_ENGINE_PDL");
+    enabled = (text != nullptr && text[0] == '0') ? 0 : 1;
+  }
+  return enabled;
+}
+
+// Launch `kernel` as a dependent of the kernel before it on `stream`.  Only for kernels that
+// call pdl_wait() before their first access to global memory another kernel may write.
+template <typename... KArgs, typename... Args>
+static inline int fe_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = fe_pdl_enabled();
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
   float* dst = out + (size_t)row * hidden;
@@ -29,9 +31,9 @@ FE_EXPORT int fe_embedding(const int* ids, const void* table, int table_dtype, f
   if (n <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == FE_DTYPE_F32)
-    embedding_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, status);
+    return fe_launch_dependent(embedding_kernel<float>, dim3(n), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, status);
   else if (table_dtype == FE_DTYPE_BF16)
-    embedding_kernel<bf16><<<n, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, status);
+    return fe_launch_dependent(embedding_kernel<bf16>, dim3(n), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, status);
   else
     return FE_ERR_BAD_DTYPE;
   return fe_last_error();
@@ -50,6 +52,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __res
   // PER > 0: every thread keeps its PER elements (strided by blockDim) in registers between
   // the two passes; PER == 0: rows too long for that are read twice.
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = row_map ? row_map[r] : r;
   float* res = residual + (size_t)src * size;
@@ -100,16 +104,17 @@ FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dty
   int threads = 32;
   while (threads < 512 && threads * 4 < size) threads <<= 1;
   const int per = (size + threads - 1) / threads;
+  int rc = 0;
 #define LAUNCH(TU, TO)                                                                               \
   do {                                                                                               \
     if (per <= 4)                                                                                    \
-      add_rmsnorm_kernel<TU, TO, 4><<<rows, threads, 0, stream>>>(residual, (const TU*)update,      \
+      rc = fe_launch_dependent(add_rmsnorm_kernel<TU, TO, 4>, dim3(rows), dim3(threads), 0, stream, residual, (const TU*)update,      \
           weight, (TO*)out, row_map, size, eps, write_residual);                                     \
     else if (per <= 16)                                                                              \
-      add_rmsnorm_kernel<TU, TO, 16><<<rows, threads, 0, stream>>>(residual, (const TU*)update,     \
+      rc = fe_launch_dependent(add_rmsnorm_kernel<TU, TO, 16>, dim3(rows), dim3(threads), 0, stream, residual, (const TU*)update,     \
           weight, (TO*)out, row_map, size, eps, write_residual);                                     \
     else                                                                                             \
-      add_rmsnorm_kernel<TU, TO, 0><<<rows, threads, 0, stream>>>(residual, (const TU*)update,      \
+      rc = fe_launch_dependent(add_rmsnorm_kernel<TU, TO, 0>, dim3(rows), dim3(threads), 0, stream, residual, (const TU*)update,      \
           weight, (TO*)out, row_map, size, eps, write_residual);                                     \
   } while (0)
   if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH(float, float);
@@ -118,7 +123,7 @@ FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dty
   else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_F32) LAUNCH(bf16, float);
   else return FE_ERR_BAD_DTYPE;
 #undef LAUNCH
-  return fe_last_error();
+  return rc ? rc : fe_last_error();
 }
 
 // ---------------------------------------------------------------------------
@@ -135,6 +140,8 @@ __device__ __forceinline__ void silu_sources(int i, int inter, int block, int* g
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const T* g = gate_up + (size_t)row * 2 * inter;
   T* o = out + (size_t)row * inter;
@@ -147,6 +154,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 
 template <typename T>
 __global__ void silu_mul_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const T* g = gate_up + (size_t)row * 2 * inter;
   T* o = out + (size_t)row * inter;
@@ -172,11 +181,11 @@ FE_EXPORT int fe_silu_mul(const void* gate_up, void* out, int dtype, int rows, i
   dim3 grid(rows, (inter + threads * per - 1) / (threads * per));
   if (grid.y > 65535) return FE_ERR_TOO_LARGE;
   if (dtype == FE_DTYPE_F32) {
-    if (vec) silu_mul_vec8_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, block);
-    else silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, block);
+    if (vec) return fe_launch_dependent(silu_mul_vec8_kernel<float>, grid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, block);
+    else return fe_launch_dependent(silu_mul_kernel<float>, grid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, block);
   } else if (dtype == FE_DTYPE_BF16) {
-    if (vec) silu_mul_vec8_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, block);
-    else silu_mul_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, block);
+    if (vec) return fe_launch_dependent(silu_mul_vec8_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, block);
+    else return fe_launch_dependent(silu_mul_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, block);
   } else {
     return FE_ERR_BAD_DTYPE;
   }

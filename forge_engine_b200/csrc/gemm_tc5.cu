@@ -163,7 +163,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
     const float r = v[j] + b;
     if (EPI == EPI_STORE_BF16) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(r);
     else if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(p.y)[at] = r;
-    else reinterpret_cast<float*>(p.y)[at] += r;
+    else reinterpret_cast<float*>(p.y)[at] = __ldcg(reinterpret_cast<const float*>(p.y) + at) + r;
   }
 }
 
@@ -211,9 +211,20 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
 
+  pdl_trigger();   // the kernel after this one may begin its own weight prefetch
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < my_blocks; ++i) {
+      // Weights do not depend on the kernel before this one: fill the ring with weight
+      // tiles first, then wait for that kernel, then fetch the token tiles.
+      const int ahead = min(STAGES, my_blocks);
+      for (int i = 0; i < ahead; ++i) {
+        mbar_expect_tx(full + i, A_BYTES + B_BYTES);
+        tma_load_2d(a_tiles + i * A_BYTES, &map_w, (kb_begin + i) * BK, m0, full + i);
+      }
+      pdl_wait();
+      for (int i = 0; i < ahead; ++i)
+        tma_load_2d(b_tiles + i * B_BYTES, &map_x, (kb_begin + i) * BK, n0, full + i);
+      for (int i = ahead; i < my_blocks; ++i) {
         const int s = i % STAGES;
         const unsigned parity = ((i / STAGES) & 1) ^ 1;
         if (!mbar_wait(empty + s, parity, abort_flag)) break;
@@ -249,6 +260,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int quarter = warp & 3;
     const int feature = m0 + quarter * 32 + lane;
     mbar_wait(acc_done, 0, abort_flag);
+    pdl_wait();   // returns at once after the producer's wait; orders this warp's own global accesses
     // all four epilogue warps take the same path: agree on the outcome of the wait
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const bool ok = *abort_flag == 0;
@@ -362,7 +374,8 @@ int launch_one(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_tc5_kernel<BN, EPI><<<grid, THREADS, smem_bytes<BN>(), stream>>>(mw, mx, p);
+  const int rc = fe_launch_dependent(gemm_tc5_kernel<BN, EPI>, grid, dim3(THREADS), smem_bytes<BN>(), stream, mw, mx, p);
+  if (rc) return rc;
   return fe_last_error();
 }
 

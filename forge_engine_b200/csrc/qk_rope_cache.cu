@@ -18,6 +18,8 @@ __global__ void qk_rope_cache_kernel(T* __restrict__ qkv, const float* __restric
                                      const int* __restrict__ positions,
                                      const int* __restrict__ token_entry, PagedKV cache,
                                      int num_q_heads, int write_kv, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int warps = (blockDim.x >> 5) * gridDim.y;             // warps working on this token
@@ -113,10 +115,10 @@ FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, cons
   if (blocks_y > 65535) return FE_ERR_TOO_LARGE;
   dim3 grid(n_tokens, blocks_y);
   if (dtype == FE_DTYPE_F32)
-    qk_rope_cache_kernel<float><<<grid, warps * 32, 0, stream>>>((float*)qkv, q_weight, k_weight,
+    return fe_launch_dependent(qk_rope_cache_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)qkv, q_weight, k_weight,
         eps, inv_freq, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
   else if (dtype == FE_DTYPE_BF16)
-    qk_rope_cache_kernel<bf16><<<grid, warps * 32, 0, stream>>>((bf16*)qkv, q_weight, k_weight,
+    return fe_launch_dependent(qk_rope_cache_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (bf16*)qkv, q_weight, k_weight,
         eps, inv_freq, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
   else
     return FE_ERR_BAD_DTYPE;

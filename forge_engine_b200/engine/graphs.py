@@ -26,11 +26,32 @@ def _bucket(value: int, floor: int = 1) -> int:
 
 
 class _CapturedStep:
+    """One captured graph with its fixed device buffer and a small ring of pinned host
+    buffers the step's integers are staged in (a ring, so that a buffer is not rewritten
+    while the copy of an earlier step may still be reading it)."""
+
+    RING = 4
+
     def __init__(self, graph, buffer, logits, launches) -> None:
         self.graph = graph
         self.buffer = buffer
         self.logits = logits
         self.launches = launches
+        self.staging = [torch.empty(buffer.numel(), dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.views = [t.numpy() for t in self.staging]
+        self.events = [None] * self.RING
+        self.turn = 0
+
+    def upload(self, flat: list) -> None:
+        slot = self.turn % self.RING
+        self.turn += 1
+        if self.events[slot] is not None:
+            self.events[slot].synchronize()
+        self.views[slot][:] = flat
+        self.buffer.copy_(self.staging[slot], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.events[slot] = event
 
 
 class DecodeGraphs:
@@ -96,8 +117,7 @@ class DecodeGraphs:
             self.captured[key] = step
         plan = self._plan(full, *key)
         assert len(plan.flat) == step.buffer.numel()
-        host = torch.tensor(plan.flat, dtype=torch.int32).pin_memory()
-        step.buffer.copy_(host, non_blocking=True)
+        step.upload(plan.flat)
         step.graph.replay()
         native.LAUNCHES += step.launches
         if len(wanted) == len(entries):

@@ -87,7 +87,7 @@ def attention_lib(head_dim: int):
             raise CUDAUnavailableError(f"cannot load {path}: {error}") from error
         fn = getattr(handle, f"fe_attention_mma_d{head_dim}")
         p, i, f = c_void_p, c_int, c_float
-        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, f, i, i, p, p, p]
+        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, f, i, i, p, p, p, p]
         fn.restype = c_int
         _attention_libs[head_dim] = fn
     return fn
@@ -263,6 +263,18 @@ def attention_simt(
     )
 
 
+_attn_counters: dict = {}
+
+
+def _attention_counters(device, pairs: int) -> torch.Tensor:
+    """Zeroed arrival counters, one per (entry, kv head); launches leave them zeroed."""
+    counters = _attn_counters.get(device)
+    if counters is None or counters.numel() < pairs:
+        counters = torch.zeros(max(pairs, 8192), dtype=torch.int32, device=device)
+        _attn_counters[device] = counters
+    return counters
+
+
 ATTN_DECODE_ROWS = 16  # rows (new tokens x heads per kv head) the split decode kernel takes
 
 
@@ -284,6 +296,7 @@ def attention_mma(
     run_prefill: bool,
     run_decode: bool,
     num_splits: int = 1,
+    merge_in_kernel: bool = True,
 ) -> None:
     """Tensor-core paged attention (bfloat16).  Entries with more than 16 rows (new
     tokens x heads per kv head) go to the prefill kernel, the others to the split
@@ -292,16 +305,18 @@ def attention_mma(
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     groups = num_q_heads // nkv
     mode = (1 if run_prefill else 0) | (2 if run_decode else 0)
-    workspace = None
+    workspace = counters = None
     if run_decode and num_splits > 1:
         floats = entries * nkv * num_splits * ATTN_DECODE_ROWS * (head_dim + 2)
         workspace = torch.empty(floats, dtype=torch.float32, device=q.device)
+        if merge_in_kernel:
+            counters = _attention_counters(q.device, entries * nkv)
     check(
         attention_lib(head_dim)(
             ptr(q), int(q_stride), ptr(out), ptr(k_cache), ptr(v_cache), ptr(block_table),
             block_table.shape[1], page_size, num_pages, nkv, groups, ptr(cu_tokens), ptr(starts),
             entries, int(max_new), int(window or 0), float(scale), mode, int(num_splits),
-            ptr(workspace), ptr(status), stream(),
+            ptr(workspace), ptr(counters), ptr(status), stream(),
         ),
         "attention_mma",
     )

@@ -18,10 +18,22 @@ from .base import BuildContext, CacheView, Mixer, WeightInfo, build_part, regist
 from .linear import Linear, fuse_rows
 
 
-# The split decode kernel is launched with about this many blocks (4 per SM of a B200),
-# so that few requests with long contexts still fill the machine.
-SPLIT_TARGET_BLOCKS = 592
-MAX_SPLITS = 64   # what the merge kernel takes; every split gets at least two 64-key tiles
+# Two blocks of the split decode kernel fit on an SM (148 SMs on a B200).
+DECODE_SLOTS = 296
+MAX_SPLITS = 64   # what the merge takes
+
+
+def choose_splits(pairs: int, tiles: int) -> int:
+    """How many blocks share one (request, kv head)'s keys.
+
+    Few pairs: fill the machine's slots once, every block getting at least two 64-key
+    tiles.  With more pairs than half the slots the machine is full anyway and splitting
+    only adds partial results to combine (measured: one split is fastest at 512 pairs of
+    2,048 keys; very long contexts take two)."""
+    most = max(1, min(MAX_SPLITS, tiles // 2))
+    if pairs * 2 > DECODE_SLOTS:
+        return 1 if tiles <= 64 else min(most, 2)
+    return max(1, min(most, DECODE_SLOTS // pairs))
 
 
 class GQAttention(Mixer):
@@ -114,8 +126,8 @@ class GQAttention(Mixer):
             if self.spec.window:
                 longest = min(longest, self.spec.window + limit)
             tiles = -(-longest // 64)
-            blocks = len(small) * self.nkv
-            splits = max(1, min(-(-tiles // 2), MAX_SPLITS, -(-SPLIT_TARGET_BLOCKS // blocks)))
+            pairs = len(small) * self.nkv
+            splits = choose_splits(pairs, tiles)
         native.attention_mma(
             qkv, qkv.shape[1], k_cache, v_cache, table, batch.cu_tokens, batch.starts,
             batch.n_entries, batch.max_new, self.spec.window, self.spec.scale, out, self.nq,

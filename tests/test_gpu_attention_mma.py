@@ -20,7 +20,7 @@ def native():
     return module
 
 
-def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, sharp=False):
+def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, sharp=False, merge_in_kernel=True):
     """Request r holds lengths[r] keys after the step, the last new_counts[r] of them new."""
     dtype = torch.bfloat16
     k_cache, v_cache, table, keys, values = paged_layout(lengths, page, nkv, d, dtype, seed=d + nq + page)
@@ -43,6 +43,7 @@ def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, shar
         torch.tensor(cu, dtype=torch.int32, device=DEV), torch.tensor(starts, dtype=torch.int32, device=DEV),
         len(lengths), max(new_counts), window, d ** -0.5, out, nq, status,
         run_prefill=any(r > 16 for r in rows), run_decode=any(r <= 16 for r in rows), num_splits=splits,
+        merge_in_kernel=merge_in_kernel,
     )
     assert int(status.item()) == 0
     for r, (n, c) in enumerate(zip(lengths, new_counts)):
@@ -69,6 +70,8 @@ def test_split_decode_long_contexts(native, splits) -> None:
     lengths = [2048, 1, 777, 64, 65, 4000]
     run_case(native, 32, 8, 128, 16, None, lengths, [1] * 6, splits)
     run_case(native, 32, 8, 128, 16, 500, lengths, [1] * 6, splits)
+    # the splits combined by a second kernel instead of by the block that arrives last
+    run_case(native, 32, 8, 128, 16, None, lengths, [1] * 6, splits, merge_in_kernel=False)
 
 
 def test_rows_do_not_depend_on_the_batch(native) -> None:
