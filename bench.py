@@ -109,16 +109,95 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def reference_arm() -> int:
-    """The upstream project's public API loads one pinned Hugging Face checkpoint by
-    download; there is no network and no local copy, and it has no random-weights mode."""
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "upstream serves only the pinned Hub checkpoint Qwen/Qwen3-4B-Instruct-2507 "
-                       "(src/forge_engine/weights.py:55-70 downloads it); no network, no local snapshot, "
-                       "and its loader rejects any other config or random weights",
-    }))
-    return 0
+def reference_arm(args) -> int:
+    """Decode tokens per second of the unmodified upstream engine at the same shape.
+
+    Upstream's loader only accepts its pinned Hub checkpoint (src/forge_engine/weights.py:55-70
+    downloads it; there is no network here) and it has no random-weights mode.  What it
+    does expose publicly is ``ConcurrentGenerationEngine(tokenizer, model, sampling params,
+    scheduler config)`` (src/forge_engine/scheduler.py:137-170) and its own
+    ``Qwen3ForCausalLM(Qwen3Config(...))``; its tests drive exactly this constructor with a
+    stub tokenizer (tests/test_scheduler.py:42-68).  So the arm builds upstream's model
+    class with the benchmark's sizes (torch's default random initialisation, bfloat16),
+    a stub tokenizer that returns synthetic ids, and times upstream's own ``step()``.
+    """
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "forge_engine").is_dir():
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference)"}))
+        return 0
+    try:
+        import torch
+
+        sys.path.insert(0, str(ref_root))
+        from forge_engine.qwen3 import Qwen3Config, Qwen3ForCausalLM
+        from forge_engine.sampling import SamplingParams
+        from forge_engine.scheduler import ConcurrentGenerationEngine, SchedulerConfig
+
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device")
+        raw = dict(CONFIG_4B)
+        if args.layers:
+            raw["num_hidden_layers"] = args.layers
+        batch, steps, warmup = args.batch, args.steps, max(3, args.warmup)
+        config = Qwen3Config(
+            vocab_size=raw["vocab_size"], hidden_size=raw["hidden_size"], intermediate_size=raw["intermediate_size"],
+            num_hidden_layers=raw["num_hidden_layers"], num_attention_heads=raw["num_attention_heads"],
+            num_key_value_heads=raw["num_key_value_heads"], head_dim=raw["head_dim"],
+            max_position_embeddings=raw["max_position_embeddings"], rms_norm_eps=raw["rms_norm_eps"],
+            rope_theta=raw["rope_theta"], eos_token_id=0, tie_word_embeddings=True, attention_bias=False)
+        torch.manual_seed(0)
+        with torch.device("cuda:0"):
+            model = Qwen3ForCausalLM(config).to(torch.bfloat16).eval()
+        generator = torch.Generator().manual_seed(5)
+
+        class StubTokenizer:
+            eos_token_id = None
+
+            def apply_chat_template(self, conversation, *, tokenize, add_generation_prompt, return_tensors):
+                return torch.randint(0, raw["vocab_size"], (1, CONTEXT), generator=generator)
+
+            def decode(self, token_ids, *, skip_special_tokens):
+                return " ".join(str(t) for t in token_ids)
+
+        total = CONTEXT + warmup + steps + 8
+        engine = ConcurrentGenerationEngine(
+            StubTokenizer(), model, SamplingParams(max_new_tokens=warmup + steps + 4),
+            SchedulerConfig(max_requests=batch, max_batch_size=batch, token_budget=batch * CONTEXT,
+                            block_size=PAGE, block_capacity=batch * (-(-total // PAGE))))
+        for i in range(batch):
+            engine.submit([{"role": "user", "content": str(i)}])
+        engine.step()                              # all prompts (one length, one forward)
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        sampler = ClockSampler()
+        sampler.start()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            engine.step()
+        end.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        ms = begin.elapsed_time(end) / steps
+        clocks = sampler.stop()
+        print(json.dumps({
+            "impl": "reference",
+            "metric": "decode tok/s (Qwen3-4B shape, bf16, batch 8, 2048-token contexts)",
+            "value": round(batch / (ms / 1e3), 2), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic token ids (seed 5), upstream model class with torch default init (seed 0)",
+            "config": {"model": "Qwen3-4B shape", "layers": raw["num_hidden_layers"], "layers_full": CONFIG_4B["num_hidden_layers"],
+                       "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE,
+                       "api": "ConcurrentGenerationEngine.step with a stub tokenizer"},
+            "clocks": clocks,
+            "e2e": {"value": round(batch * steps / wall, 2), "unit": "tokens/s", "ms_per_step": round(1e3 * wall / steps, 4)},
+        }))
+        return 0
+    except Exception as error:  # the arm must never fail the run
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(error).__name__}: {str(error)[:200]}"}))
+        return 0
 
 
 def main() -> int:
@@ -130,9 +209,14 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1/64, prefill and e2e")
+    parser.add_argument("--prefill-only", action="store_true",
+                        help="time only the 2,048-token prefill (small cases for profiling)")
     args = parser.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        if args.gpus != 1:
+            print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
+            return 2
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
         return 2
@@ -197,6 +281,35 @@ def main() -> int:
             runner.end(key)
         return ms, clocks, launches
 
+    def prefill_run(repeats: int) -> dict:
+        """One 2,048-token prompt in one step, logits at its last place."""
+        prompt = torch.randint(0, raw["vocab_size"], (CONTEXT,), generator=gen).tolist()
+        times = []
+        for i in range(3 + repeats):
+            key = f"p{i}"
+            runner.begin(key)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record()
+            runner.step([StepEntry(key, prompt, [CONTEXT - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(begin.elapsed_time(end))
+            runner.end(key)
+        ms_prefill = statistics.median(times)
+        h, q = raw["hidden_size"], raw["num_attention_heads"] * raw["head_dim"]
+        kv, inter = raw["num_key_value_heads"] * raw["head_dim"], raw["intermediate_size"]
+        linear = 2 * CONTEXT * layers * (h * (q + 2 * kv) + q * h + 3 * h * inter) + 2 * raw["vocab_size"] * h
+        attention = layers * 4 * raw["num_attention_heads"] * raw["head_dim"] * CONTEXT * (CONTEXT + 1) // 2
+        flops = linear + attention
+        return {"value": round(CONTEXT / (ms_prefill / 1e3), 1), "tokens": CONTEXT, "ms": round(ms_prefill, 3),
+                "frac": round(flops / (ms_prefill / 1e3) / (bf16_tflops * 1e12), 4), "flops": flops}
+
+    if args.prefill_only:
+        print(json.dumps({"prefill": prefill_run(max(1, args.steps)), "layers": layers, "impl": "ours"}))
+        return 0
+
     ms_step, clocks, launches = decode_run(args.batch, args.steps, args.warmup)
     value = args.batch / (ms_step / 1e3)
     step_bytes = weight_bytes + args.batch * (CONTEXT + args.warmup + args.steps / 2) * kv_bytes_per_token
@@ -247,31 +360,7 @@ def main() -> int:
             points[f"decode_b{batch}"] = round(batch / (ms / 1e3), 2)
         record["points"] = points
 
-        # prefill: one 2,048-token prompt in one step, logits at its last place
-        prompt = torch.randint(0, raw["vocab_size"], (CONTEXT,), generator=gen).tolist()
-        times = []
-        for i in range(3 + 3):
-            key = f"p{i}"
-            runner.begin(key)
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            begin.record()
-            runner.step([StepEntry(key, prompt, [CONTEXT - 1])])
-            end.record()
-            torch.cuda.synchronize()
-            if i >= 3:
-                times.append(begin.elapsed_time(end))
-            runner.end(key)
-        ms_prefill = statistics.median(times)
-        h, q = raw["hidden_size"], raw["num_attention_heads"] * raw["head_dim"]
-        kv, inter = raw["num_key_value_heads"] * raw["head_dim"], raw["intermediate_size"]
-        linear = 2 * CONTEXT * layers * (h * (q + 2 * kv) + q * h + 3 * h * inter) + 2 * raw["vocab_size"] * h
-        attention = layers * 4 * raw["num_attention_heads"] * raw["head_dim"] * CONTEXT * (CONTEXT + 1) // 2
-        flops = linear + attention
-        record["prefill"] = {
-            "value": round(CONTEXT / (ms_prefill / 1e3), 1), "tokens": CONTEXT, "ms": round(ms_prefill, 3),
-            "frac": round(flops / (ms_prefill / 1e3) / (bf16_tflops * 1e12), 4), "flops": flops,
-        }
+        record["prefill"] = prefill_run(3)
 
         # end to end through the Python entry point: host ids in, sampled ids out, every step
         del runner

@@ -241,9 +241,12 @@ __device__ __forceinline__ void load_q_rows(bf16* qs, const AttnParams& p, int t
 
 __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LD]
-  bf16* kbuf = qs + BM * LD;                      // [2][BN][LD]
-  bf16* vbuf = kbuf + 2 * BN * LD;                // [2][BN][LD]
+  // Two key/value stages.  The query tile is staged in the second stage's buffers, read
+  // into registers once, and the space is then used for keys and values: three blocks
+  // fit on an SM instead of two.
+  bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);   // [2][BN][LD]
+  bf16* vbuf = kbuf + 2 * BN * LD;                  // [2][BN][LD]
+  bf16* qs = kbuf + BN * LD;                        // [BM][LD] over stage 1 (BM == BN)
 
   pdl_trigger();
   pdl_wait();
@@ -252,7 +255,9 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   const int n_new = p.cu_tokens[entry + 1] - tok0;
   const int rows_total = n_new * p.groups;
   if (rows_total <= p.row_lo || rows_total > p.row_hi) return;
-  const int row0 = blockIdx.x * BM;
+  // Later row tiles see more keys and run longer: start them first so that the last
+  // round of blocks is made of short ones.
+  const int row0 = (gridDim.x - 1 - blockIdx.x) * BM;
   if (row0 >= rows_total) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int start = p.starts[entry];
@@ -268,6 +273,13 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   load_q_rows(qs, p, tok0, kvh, row0, rows_total, BM, tid, THREADS);
   load_kv_tile(kbuf, vbuf, p, table, kvh, tile_begin * BN, key_lo, key_end, tid);
   cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  unsigned qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk)
+    ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+  __syncthreads();   // the query tile's space may now take keys
 
   const int ra = row0 + warp * 16 + (lane >> 2), rb = ra + 8;
   const int pos_a = ra < rows_total ? start + ra / p.groups : -1;
@@ -282,7 +294,6 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
   float o[D / 8][4];
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
-  unsigned qf[D / 16][4];
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int buf = (tile - tile_begin) & 1;
@@ -295,11 +306,6 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(AttnParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (tile == tile_begin) {
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk)
-        ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
-    }
     const int key0 = tile * BN;
     // keys of this tile that no row of the warp can see are skipped altogether
     if (wrow0 < rows_total && key0 <= wpos_max) {
@@ -562,7 +568,8 @@ __global__ void __launch_bounds__(THREADS) attn_merge_kernel(AttnParams p) {
   }
 }
 
-constexpr size_t PREFILL_SMEM = (size_t)(BM + 4 * BN) * LD * sizeof(bf16);
+static_assert(BM == BN, "the query tile is staged in one key stage");
+constexpr size_t PREFILL_SMEM = (size_t)(4 * BN) * LD * sizeof(bf16);
 constexpr size_t DECODE_KV_SMEM = (size_t)(DEC_ROWS + 2 * DEC_STAGES * BN) * LD * sizeof(bf16);
 constexpr size_t DECODE_MERGE_SMEM =
     (size_t)DEC_ROWS * LD * sizeof(bf16) + (size_t)4 * DEC_ROWS * (D + 2) * sizeof(float) +
