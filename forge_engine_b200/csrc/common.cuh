@@ -116,20 +116,35 @@ static inline int fe_pdl_enabled() {
 
 // Launch `kernel` as a dependent of the kernel before it on `stream`.  Only for kernels that
 // call pdl_wait() before their first access to global memory another kernel may write.
+// cluster_z > 1 additionally groups that many consecutive blocks along z into one
+// thread-block cluster (they can then read one another's shared memory).
 template <typename... KArgs, typename... Args>
-static inline int fe_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                      cudaStream_t stream, Args&&... args) {
+static inline int fe_launch_dependent_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                              cudaStream_t stream, int cluster_z, Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
+  cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = fe_pdl_enabled();
   config.attrs = attribute;
   config.numAttrs = 1;
+  if (cluster_z > 1) {
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = 1;
+    attribute[1].val.clusterDim.y = 1;
+    attribute[1].val.clusterDim.z = (unsigned)cluster_z;
+    config.numAttrs = 2;
+  }
   return (int)cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline int fe_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args&&... args) {
+  return fe_launch_dependent_cluster(kernel, grid, block, smem, stream, 1, std::forward<Args>(args)...);
 }
 
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

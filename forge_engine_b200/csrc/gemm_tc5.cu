@@ -13,9 +13,11 @@
 //                     warps 2-5  epilogue: tcgen05.ld of their 32 accumulator lanes
 //                             (lane = output feature, column = token), bias / SiLU*mul /
 //                             residual add, coalesced stores along the feature dimension
-//   grid (feature tiles, token tiles, k-splits).  With k-splits > 1 every block writes its
-//   partial tile to a workspace; the block that arrives last adds them in split order and
-//   runs the epilogue, so results do not depend on timing.
+//   grid (feature tiles, token tiles, k-splits).  With k-splits > 1 the blocks of one tile
+//   add their partial tiles in split order, so results do not depend on timing: up to 8
+//   splits form a thread-block cluster and its first block reads the others' partial tiles
+//   from their shared memory; beyond that (or for wide token tiles) partial tiles go
+//   through a workspace and the block that arrives last adds them.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the block sets a bit in the
 // status word, stops issuing work, frees its tensor memory and returns.
@@ -39,6 +41,7 @@ struct GemmParams {
   int n, o, k;
   int epilogue;
   int ksplit;
+  int cluster_reduce;    // k-splits of a tile form a cluster and add their partial tiles through shared memory
   float* ws_part;        // [feature tiles, token tiles, ksplit, BN, BM] floats
   unsigned* ws_count;    // [feature tiles * token tiles], zero before and after a launch
   int* status;
@@ -128,9 +131,9 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 
 template <int BN> __host__ __device__ constexpr int stages_for() {
   // stage = weight tile (16 KB) + token tile (BN * 128 B).  Narrow token tiles keep the ring
-  // small enough for three (BN <= 16) or two blocks per SM, so that one block's epilogue and
-  // set-up overlap another's streaming; the widest tile takes the SM alone.
-  return BN <= 128 ? (BN == 128 ? 3 : 4) : 4;
+  // at about 100 KB, two blocks per SM, so that one block's epilogue and set-up overlap
+  // another's streaming; the widest tile takes the SM alone.
+  return BN <= 32 ? 6 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4));
 }
 
 // Finished values of one accumulator row (feature) for 16 consecutive tokens.
@@ -278,6 +281,22 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
         store16<EPI>(p, v, feature, n0 + c, lane);
       }
+    } else if (ok && p.cluster_reduce) {
+      // stash the partial tile in this block's shared memory ([token][feature], over the
+      // first weight stages, which nobody reads any more); the cluster's first block adds
+      // the stashes below
+      float* stash = reinterpret_cast<float*>(a_tiles);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        if (my_blocks > 0) tmem_ld16(lane_base + c, v);
+        else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stash[(c + j) * BM + quarter * 32 + lane] = v[j];
+      }
     } else if (ok) {
       // publish the partial tile: ws[tile][split][token][feature]
       const size_t tile = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
@@ -321,6 +340,38 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
   }
 
+  if (p.cluster_reduce) {
+    // every thread of every block of the cluster takes part in both barriers
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    unsigned rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    if (rank == 0 && warp >= 2 && *abort_flag == 0) {
+      const int quarter = warp & 3;
+      const int feature = m0 + quarter * 32 + lane;
+      const unsigned local = smem_u32(a_tiles);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        for (int peer = 0; peer < p.ksplit; ++peer) {     // fixed order: the sum does not depend on timing
+          unsigned remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(peer));
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float part;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                         : "=f"(part) : "r"(remote + (unsigned)(((c + j) * BM + quarter * 32 + lane) * 4)) : "memory");
+            v[j] += part;
+          }
+        }
+        store16<EPI>(p, v, feature, n0 + c, lane);
+      }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // stashes stay alive until read
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -374,7 +425,8 @@ int launch_one(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int rc = fe_launch_dependent(gemm_tc5_kernel<BN, EPI>, grid, dim3(THREADS), smem_bytes<BN>(), stream, mw, mx, p);
+  const int rc = fe_launch_dependent_cluster(gemm_tc5_kernel<BN, EPI>, grid, dim3(THREADS), smem_bytes<BN>(), stream,
+                                             p.cluster_reduce ? p.ksplit : 1, mw, mx, p);
   if (rc) return rc;
   return fe_last_error();
 }
@@ -409,14 +461,15 @@ FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void*
   if (ksplit < 1) ksplit = 1;
   const int kblocks = (k + BK - 1) / BK;
   if (ksplit > kblocks) ksplit = kblocks;
-  if (ksplit > 1 && (ws_part == nullptr || ws_count == nullptr)) return FE_ERR_BAD_SHAPE;
   const int bn = fe_gemm_tc5_tile(n);
+  if (ksplit > 1 && !(ksplit <= 8 && bn <= 64) && (ws_part == nullptr || ws_count == nullptr)) return FE_ERR_BAD_SHAPE;
   CUtensorMap mw, mx;
   int rc = make_map(&mw, w, o, k, BM);
   if (rc) return rc;
   rc = make_map(&mx, x, n, k, bn);
   if (rc) return rc;
-  GemmParams p{y, bias, n, o, k, epilogue, ksplit, ws_part, ws_count, status};
+  const int cluster_reduce = (ksplit > 1 && ksplit <= 8 && bn <= 64) ? 1 : 0;
+  GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, ws_part, ws_count, status};
   dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
   if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;
   switch (bn) {

@@ -62,7 +62,6 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_attention_simt": [p, i, i, p, p, p, i, i, i, p, p, i, f, p, i, i, i, i, p, p],
         "fe_gemm_simt": [p, i, p, i, p, p, i, i, i, i, i, p],
         "fe_sample": [p, i, i, p, p, p, p, p, p, p, p, p],
-        "fe_gemm_skinny": [p, p, p, p, i, i, i, i, i, p, p, p],
         "fe_gemm_tc5": [p, p, p, p, i, i, i, i, i, p, p, p, p],
     }
     for name, argtypes in signatures.items():
@@ -342,60 +341,6 @@ def gemm_simt(
     )
 
 
-SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ADD_F32, SKINNY_SILU_MUL = 0, 1, 2, 3
-SKINNY_MAX_ROWS = 64
-
-
-_skinny_scratch: dict = {}
-
-
-def _skinny_workspace(device, tiles: int, ksplit: int):
-    """Partial-tile buffer and arrival counters for split-k launches on ``device``.  The
-    counters are zeroed once; every launch leaves them zeroed again."""
-    entry = _skinny_scratch.get(device)
-    need_part, need_count = tiles * ksplit * 16 * 64, tiles
-    if entry is None or entry[0].numel() < need_part or entry[1].numel() < need_count:
-        part = torch.empty(max(need_part, 1 << 20), dtype=torch.float32, device=device)
-        count = torch.zeros(max(need_count, 16384), dtype=torch.int32, device=device)
-        entry = (part, count)
-        _skinny_scratch[device] = entry
-    return entry
-
-
-def skinny_ksplit(o: int, k: int) -> int:
-    """Blocks per 16-feature tile so that a small matrix still fills the machine."""
-    tiles = -(-o // 16)
-    if tiles >= 592:
-        return 1
-    return max(1, min(8, 592 // tiles, k // 2048 if k >= 4096 else k // 1024))
-
-
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
-                bias: torch.Tensor | None = None, ksplit: int | None = None) -> None:
-    """out = x @ w.T for at most 64 rows of x (bfloat16 operands, weights streamed once).
-
-    epilogue 0: out bf16 [n, o]; 1: out f32 [n, o]; 2: out f32 [n, o] += product;
-    3: out bf16 [n, o/2] = silu(gate) * up for w whose rows alternate 8 gate, 8 up features."""
-    _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
-    n, k = x.shape
-    o = w.shape[0]
-    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
-    if epilogue == SKINNY_SILU_MUL:
-        assert out.shape == (n, o // 2) and out.dtype == torch.bfloat16
-    else:
-        assert out.shape == (n, o)
-        assert out.dtype == (torch.bfloat16 if epilogue == SKINNY_STORE_BF16 else torch.float32)
-    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == o)
-    if ksplit is None:
-        ksplit = skinny_ksplit(o, k)
-    part = count = None
-    if ksplit > 1:
-        part, count = _skinny_workspace(x.device, -(-o // 16), ksplit)
-    check(lib().fe_gemm_skinny(ptr(x), ptr(w), ptr(bias), ptr(out), n, o, k, int(epilogue), int(ksplit),
-                               ptr(part), ptr(count), stream()),
-          "gemm_skinny")
-
-
 TC5_STORE_BF16, TC5_STORE_F32, TC5_ADD_F32, TC5_SILU_MUL = 0, 1, 2, 3
 _tc5_scratch: dict = {}
 
@@ -419,10 +364,12 @@ TC5_MAX_ROWS = 64   # up to this many rows the tcgen05 kernel is used instead of
 
 
 def tc5_ksplit(o: int, k: int) -> int:
-    """Blocks per output tile: enough blocks to cover the SMs when the weight has few
-    128-row tiles, never so many that a block gets less than eight 64-wide k-blocks."""
+    """Blocks per 128-feature tile for few tokens.  A weight with few tiles is cut along k
+    so that about 190 blocks stream it (measured best on a B200: 4 for 48 tiles, 8 for 20);
+    up to 8 such blocks form a cluster and add their partial tiles through shared memory.
+    A block keeps at least four 64-wide k-blocks."""
     tiles = -(-o // 128)
-    return max(1, min(-(-148 // tiles), 4, (k // 64) // 8))
+    return max(1, min(8, round(192 / tiles), (k // 64) // 4))
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: torch.Tensor,

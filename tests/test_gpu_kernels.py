@@ -442,15 +442,3 @@ def test_gemm_tc5_silu_mul(native, n, inter, k, ksplit) -> None:
     native.gemm_tc5(x, w, out, native.TC5_SILU_MUL, status, ksplit=ksplit)
     torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=1e-2)
     assert int(status.item()) == 0
-
-
-@pytest.mark.parametrize("n,o,k", [(1, 331, 80), (8, 6144, 2560), (16, 400, 200), (40, 203, 136), (64, 2560, 4096)])
-def test_gemm_skinny(native, n, o, k) -> None:
-    g = torch.Generator().manual_seed(n + o)
-    x = torch.randn((n, k), generator=g).bfloat16().to(DEV)
-    w = (torch.randn((o, k), generator=g) * 0.1).bfloat16().to(DEV)
-    ref = x.double() @ w.double().t()
-    for ksplit in (1, 3):
-        out = torch.full((n, o), float("nan"), dtype=torch.float32, device=DEV)
-        native.gemm_skinny(x, w, out, native.SKINNY_STORE_F32, ksplit=ksplit)
-        torch.testing.assert_close(out.double(), ref, atol=2e-4, rtol=1e-5)
