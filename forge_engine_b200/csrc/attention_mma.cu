@@ -21,7 +21,11 @@
 // Rounding: scores and softmax statistics are 32-bit; probabilities are rounded to
 // bfloat16 for the value product (as upstream rounds them, qwen3.py:200); the row sum
 // uses the unrounded values.
+#include <cuda.h>
 #include <stdio.h>
+
+#include <map>
+#include <tuple>
 
 #include "attention_common.cuh"
 
@@ -134,7 +138,21 @@ __device__ __forceinline__ void load_kv_tile(bf16* kdst, bf16* vdst, const AttnP
 //   qf    - Q fragments of this warp's 16 rows (D/16 k-steps)
 //   ks,vs - shared tiles; this warp uses keys [koff, koff + NKEYS) of them
 //   key0  - absolute position of the first of those keys
-template <int NKEYS>
+// Where element (key, col) of a staged tile lives.  Padded: rows of LD elements (cp.async
+// path).  Swizzled: what TMA writes with 128-byte swizzle - two-dimensional boxes of 64
+// columns, so a tile is D/64 column blocks of [64 keys][128 bytes], and inside a row the
+// 16-byte chunk c sits at chunk c ^ (row & 7).
+struct PaddedTile {
+  static __device__ __forceinline__ const bf16* at(const bf16* base, int key, int col) { return base + key * LD + col; }
+};
+struct SwizzledTile {
+  static __device__ __forceinline__ const bf16* at(const bf16* base, int key, int col) {
+    const int block = col >> 6, chunk = (col >> 3) & 7;
+    return base + block * (BN * 64) + key * 64 + ((chunk ^ (key & 7)) << 3);
+  }
+};
+
+template <int NKEYS, typename Tile = PaddedTile>
 __device__ __forceinline__ void tile_step(const unsigned (&qf)[D / 16][4], const bf16* ks, const bf16* vs,
                                           int koff, int key0, int key_end, int pos_a, int pos_b,
                                           int window, float scale_log2, bool need_mask, float (&m)[2],
@@ -150,7 +168,7 @@ __device__ __forceinline__ void tile_step(const unsigned (&qf)[D / 16][4], const
       unsigned b[4];
       const int key = koff + j2 * 16 + (lane & 7) + ((lane >> 4) << 3);
       const int col = kk * 16 + ((lane >> 3) & 1) * 8;
-      ldmatrix_x4(b, ks + key * LD + col);
+      ldmatrix_x4(b, Tile::at(ks, key, col));
       mma_bf16(s[2 * j2], qf[kk], b[0], b[1]);
       mma_bf16(s[2 * j2 + 1], qf[kk], b[2], b[3]);
     }
@@ -216,7 +234,7 @@ __device__ __forceinline__ void tile_step(const unsigned (&qf)[D / 16][4], const
       unsigned b[4];
       const int key = koff + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
       const int col = n2 * 16 + (lane >> 4) * 8;
-      ldmatrix_x4_trans(b, vs + key * LD + col);
+      ldmatrix_x4_trans(b, Tile::at(vs, key, col));
       mma_bf16(o[2 * n2], a, b[0], b[1]);
       mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
     }
@@ -512,6 +530,276 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(AttnParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Split decode attention with the key/value tiles staged by TMA (head sizes that are
+// multiples of 64, page sizes that divide 64).  One extra warp is the producer: for every
+// 64-key tile it looks the pages up and issues one tensor copy per page and 64-column block
+// (128-byte swizzle) into a ring of stages, signalled by mbarriers; the four consumer warps
+// never issue a load and never meet at a block-wide barrier while keys stream.  Tiles that
+// only hold keys of earlier steps are requested before the wait on the previous kernel.
+// ---------------------------------------------------------------------------
+constexpr int TMA_STAGES = 3;
+constexpr int TMA_THREADS = THREADS + 32;
+constexpr unsigned TMA_WAIT_LIMIT = 20000000u;
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// Bounded wait on a phase; false (and the flag set) when the bound is hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag) {
+  for (unsigned i = 0; i < TMA_WAIT_LIMIT; ++i) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  constexpr int TILE_BYTES = BN * D * 2;    // one matrix of one stage
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  bf16* kbuf = reinterpret_cast<bf16*>(smem);                                   // [TMA_STAGES][D/64][BN][64]
+  bf16* vbuf = reinterpret_cast<bf16*>(smem + TMA_STAGES * TILE_BYTES);
+  bf16* qs = reinterpret_cast<bf16*>(smem + 2 * TMA_STAGES * TILE_BYTES);         // [16][LD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(qs + DEC_ROWS * LD);
+  uint64_t* empty = full + TMA_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + TMA_STAGES);
+  __shared__ int last_block;
+
+  pdl_trigger();
+  const int split = blockIdx.x, entry = blockIdx.y, kvh = blockIdx.z;
+  const int tok0 = p.cu_tokens[entry];
+  const int n_new = p.cu_tokens[entry + 1] - tok0;
+  const int rows_total = n_new * p.groups;
+  if (rows_total <= p.row_lo || rows_total > p.row_hi) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int start = p.starts[entry];
+  const int* table = p.block_table + (size_t)entry * p.max_pages;
+
+  const int pos_last = start + n_new - 1;
+  const int key_lo = p.window > 0 ? max(0, start - p.window + 1) : 0;
+  const int key_end = pos_last + 1;
+  const int tile_first = key_lo / BN, tile_stop = (key_end + BN - 1) / BN;
+  const int tiles = tile_stop - tile_first;
+  const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = tile_first + split * per_split;
+  const int tile_end = min(tile_stop, tile_begin + per_split);
+  const int my_tiles = max(0, tile_end - tile_begin);
+
+  if (tid == 0) {
+    for (int s = 0; s < TMA_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  const int ra = lane >> 2, rb = ra + 8;
+
+  if (warp == 4) {
+    // ---- producer ----
+    // The lanes fetch the block-table entries of up to 32 pages at once (one coalesced
+    // load instead of a chain of dependent ones); lane 0 then issues the copies.
+    if (my_tiles > 0) {
+      const int pages_per_tile = BN / p.page_size;
+      const int rows_in_cache = p.num_pages * p.nkv * p.page_size;
+      const int first_logical = tile_begin * pages_per_tile;
+      const int total_pages = my_tiles * pages_per_tile;
+      bool waited = false, dead = false;
+      for (int base = 0; base < total_pages; base += 32) {
+        const int logical = first_logical + base + lane;
+        const int key = logical * p.page_size;
+        int my_row = rows_in_cache;          // outside the tensor: the copy fills zeros
+        if (base + lane < total_pages && key < key_end) {
+          const int page = logical < p.max_pages ? table[logical] : -1;
+          if (page >= 0 && page < p.num_pages) my_row = (page * p.nkv + kvh) * p.page_size;
+          else if (key + p.page_size > key_lo) atomicOr(p.status, FE_STATUS_BAD_PAGE);
+        }
+        const int count = min(32, total_pages - base);
+        for (int j = 0; j < count; ++j) {
+          const int row = __shfl_sync(0xffffffffu, my_row, j);
+          if (lane == 0 && !dead) {
+            const int index = base + j;
+            const int i = index / pages_per_tile, pg = index - i * pages_per_tile;
+            const int s = i % TMA_STAGES;
+            if (pg == 0) {
+              const int key0 = (tile_begin + i) * BN;
+              // keys of this step are written by the kernel before this one
+              if (!waited && (key0 + BN > start || i >= TMA_STAGES)) { pdl_wait(); waited = true; }
+              if (i >= TMA_STAGES && !mbar_wait(empty + s, ((i / TMA_STAGES) & 1) ^ 1, abort_flag)) dead = true;
+              if (!dead) mbar_expect_tx(full + s, 2 * TILE_BYTES);
+            }
+            if (!dead) {
+#pragma unroll
+              for (int blk = 0; blk < D / 64; ++blk) {
+                const int offset = blk * (BN * 64) + pg * p.page_size * 64;
+                tma_load_2d(kbuf + s * (BN * D) + offset, &map_k, blk * 64, row, full + s);
+                tma_load_2d(vbuf + s * (BN * D) + offset, &map_v, blk * 64, row, full + s);
+              }
+            }
+          }
+        }
+      }
+      if (lane == 0 && !waited) pdl_wait();
+    }
+  } else {
+    // ---- consumers: warp w takes keys [16 w, 16 w + 16) of every tile ----
+    pdl_wait();
+    const int pos_a = ra < rows_total ? start + ra / p.groups : -1;
+    const int pos_b = rb < rows_total ? start + rb / p.groups : -1;
+    if (my_tiles > 0) {
+      // the four warps stage the query rows themselves (named barrier of 128 threads)
+      load_q_rows(qs, p, tok0, kvh, 0, rows_total, DEC_ROWS, tid, THREADS);
+      cp_async_commit();
+      cp_async_wait<0>();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      unsigned qf[D / 16][4];
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qf[kk], qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+      for (int i = 0; i < my_tiles; ++i) {
+        const int s = i % TMA_STAGES;
+        if (!mbar_wait(full + s, (i / TMA_STAGES) & 1, abort_flag)) break;
+        const int key0 = (tile_begin + i) * BN + warp * 16;
+        if (key0 < key_end)
+          tile_step<16, SwizzledTile>(qf, kbuf + s * (BN * D), vbuf + s * (BN * D), warp * 16, key0, key_end, pos_a,
+                                      pos_b, p.window, p.scale_log2, true, m, l, o, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+      }
+    }
+  }
+  __syncthreads();   // every load has landed and every warp is done with the stages
+
+  // merge the four consumer warps: reuse the key stages
+  float* acc_s = reinterpret_cast<float*>(kbuf);          // [4][16][D]
+  float* ml_s = acc_s + 4 * DEC_ROWS * D;                 // [4][16][2]
+  if (warp < 4) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = half ? rb : ra;
+      float* dst = acc_s + ((size_t)warp * DEC_ROWS + row) * D + 2 * (lane & 3);
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        dst[n * 8] = o[n][2 * half];
+        dst[n * 8 + 1] = o[n][2 * half + 1];
+      }
+      if ((lane & 3) == 0) {
+        ml_s[(warp * DEC_ROWS + row) * 2] = m[half];
+        ml_s[(warp * DEC_ROWS + row) * 2 + 1] = l[half];
+      }
+    }
+  }
+  __syncthreads();
+  const int num_q_heads = p.nkv * p.groups;
+  const size_t pair = (size_t)entry * p.nkv + kvh;
+  for (int idx = tid; idx < rows_total * D; idx += TMA_THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_s[(w * DEC_ROWS + row) * 2]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = ml_s[(w * DEC_ROWS + row) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - big);
+      num += acc_s[((size_t)w * DEC_ROWS + row) * D + d] * f;
+      den += ml_s[(w * DEC_ROWS + row) * 2 + 1] * f;
+    }
+    if (p.num_splits == 1) {
+      const int token = row / p.groups, g = row - token * p.groups;
+      p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
+          __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else {
+      const size_t slot = pair * p.num_splits + split;
+      p.ws_acc[(slot * DEC_ROWS + row) * D + d] = num;
+      if (d == 0) {
+        p.ws_ml[(slot * DEC_ROWS + row) * 2] = big;
+        p.ws_ml[(slot * DEC_ROWS + row) * 2 + 1] = den;
+      }
+    }
+  }
+  if (tid == 0 && *abort_flag) atomicOr(p.status, FE_STATUS_WAIT_TIMEOUT);
+  if (p.num_splits == 1) return;
+
+  // the block that publishes its partial result last combines all of them, in split order
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned arrived = atomicAdd(p.ws_count + pair, 1u);
+    last_block = arrived == (unsigned)p.num_splits - 1u;
+    if (last_block) p.ws_count[pair] = 0u;
+  }
+  __syncthreads();
+  if (!last_block) return;
+  __threadfence();
+  float* weight_s = reinterpret_cast<float*>(kbuf);       // [16][MERGE_MAX_SPLITS]
+  const int splits = p.num_splits;
+  const size_t slot0 = pair * splits;
+  for (int row = warp; row < rows_total; row += TMA_THREADS / 32) {
+    float mv[MERGE_MAX_SPLITS / 32], lv[MERGE_MAX_SPLITS / 32];
+    float big = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int sp = lane + i * 32;
+      mv[i] = -INFINITY; lv[i] = 0.f;
+      if (sp < splits) {
+        mv[i] = __ldcg(p.ws_ml + ((slot0 + sp) * DEC_ROWS + row) * 2);
+        lv[i] = __ldcg(p.ws_ml + ((slot0 + sp) * DEC_ROWS + row) * 2 + 1);
+      }
+      big = fmaxf(big, mv[i]);
+    }
+    big = warp_max(big);
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      mv[i] = (mv[i] == -INFINITY) ? 0.f : exp2f(mv[i] - big);
+      den += lv[i] * mv[i];
+    }
+    den = warp_sum(den);
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int sp = lane + i * 32;
+      if (sp < splits) weight_s[row * MERGE_MAX_SPLITS + sp] = mv[i] * inv;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows_total * D; idx += TMA_THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    const float* src = p.ws_acc + (slot0 * DEC_ROWS + row) * D + d;
+    float num = 0.f;
+#pragma unroll 4
+    for (int sp = 0; sp < splits; ++sp) num += __ldcg(src + (size_t)sp * DEC_ROWS * D) * weight_s[row * MERGE_MAX_SPLITS + sp];
+    const int token = row / p.groups, g = row - token * p.groups;
+    p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] = __float2bfloat16_rn(num);
+  }
+}
+
 // Combine the splits' (max, sum, acc) of every row: block = (entry, kv head).  The splits'
 // weights exp2(m_s - max) / sum are worked out once per row in shared memory; then every
 // thread owns one or more columns and sums over the splits with independent loads.
@@ -578,6 +866,47 @@ constexpr size_t DECODE_SMEM = DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SM
 
 }  // namespace
 
+namespace {
+
+constexpr size_t DECODE_TMA_SMEM = (size_t)2 * TMA_STAGES * BN * D * sizeof(bf16) + (size_t)DEC_ROWS * LD * sizeof(bf16) +
+                                   (size_t)2 * TMA_STAGES * 8 + 16 + 1024;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map of one cache matrix seen as [pages * kv heads * page_size rows, D columns]:
+// boxes of page_size rows x 64 columns, 128-byte swizzle, zeros outside.  Maps are kept
+// per (pointer, rows, page size): a model has two per attention layer.
+const CUtensorMap* cache_map(const void* base, int rows, int page_size) {
+  static std::map<std::tuple<const void*, int, int>, CUtensorMap> maps;
+  static EncodeTiledFn encode = nullptr;
+  const auto key = std::make_tuple(base, rows, page_size);
+  auto found = maps.find(key);
+  if (found != maps.end()) return &found->second;
+  if (encode == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return nullptr;
+    encode = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  CUtensorMap map;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
+  cuuint32_t elem[2] = {1, 1};
+  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  if (maps.size() > 4096) maps.clear();
+  return &maps.emplace(key, map).first->second;
+}
+
+}  // namespace
+
 // Workspace sizes (in floats) the decode path needs for `entries` and `num_splits`.
 FE_EXPORT long long SYM(fe_attn_workspace_floats_d)(int entries, int num_kv_heads, int num_splits) {
   return (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
@@ -633,7 +962,22 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
     if (num_splits > 1 && workspace == nullptr) return FE_ERR_BAD_SHAPE;
     p.row_lo = 0; p.row_hi = DEC_ROWS;
     dim3 grid(num_splits, entries, num_kv_heads);
-    int rc = fe_launch_dependent(attn_decode_kernel, grid, dim3(THREADS), DECODE_SMEM, stream, p);
+    int rc = 0;
+    const bool tma_ok = (D % 64) == 0 && page_size <= BN && (BN % page_size) == 0 && (num_splits == 1 || counters != nullptr);
+    const CUtensorMap* mk = tma_ok ? cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
+    const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
+    if (mk && mv) {
+      static bool tma_configured = false;
+      if (!tma_configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)DECODE_TMA_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        tma_configured = true;
+      }
+      rc = fe_launch_dependent(attn_decode_tma_kernel, grid, dim3(TMA_THREADS), DECODE_TMA_SMEM, stream, *mk, *mv, p);
+    } else {
+      rc = fe_launch_dependent(attn_decode_kernel, grid, dim3(THREADS), DECODE_SMEM, stream, p);
+    }
     if (rc) return rc;
     if (num_splits > 1 && counters == nullptr) {
       dim3 mgrid(entries, num_kv_heads);

@@ -26,11 +26,11 @@ MAX_SPLITS = 64   # what the merge takes
 def choose_splits(pairs: int, tiles: int) -> int:
     """How many blocks share one (request, kv head)'s keys.
 
-    Few pairs: fill the machine's slots once, every block getting at least two 64-key
+    Few pairs: fill the machine's slots once, every block getting at least four 64-key
     tiles.  With more pairs than half the slots the machine is full anyway and splitting
     only adds partial results to combine (measured: one split is fastest at 512 pairs of
     2,048 keys; very long contexts take two)."""
-    most = max(1, min(MAX_SPLITS, tiles // 2))
+    most = max(1, min(MAX_SPLITS, tiles // 4))
     if pairs * 2 > DECODE_SLOTS:
         return 1 if tiles <= 64 else min(most, 2)
     return max(1, min(most, DECODE_SLOTS // pairs))
