@@ -239,7 +239,9 @@ def main() -> int:
     gen = torch.Generator().manual_seed(5)
 
     max_batch = 64 if not args.skip_points else args.batch
-    steps_total = args.warmup + args.steps + 8
+    # the end-to-end run feeds one prompt a step, so requests start decoding up to `batch`
+    # steps apart; nobody may reach its length limit inside the timed region
+    steps_total = args.warmup + args.steps + 64 + 16
     pages_per_request = -(-(CONTEXT + steps_total) // PAGE) + 1
     num_pages = max_batch * pages_per_request + 8
     runner = ModelRunner.from_random(raw, 0, dtype="bfloat16", device=device, page_size=PAGE,
@@ -368,7 +370,7 @@ def main() -> int:
         e2e_steps = args.steps
         engine = Engine.from_random(
             raw, 0,
-            engine_config=EngineConfig(max_new_tokens=args.warmup + e2e_steps + 4, dtype="bfloat16"),
+            engine_config=EngineConfig(max_new_tokens=steps_total, dtype="bfloat16"),
             scheduler_config=SchedulerConfig(max_requests=args.batch, max_batch_size=args.batch,
                                              token_budget=CONTEXT + args.batch, block_size=PAGE,
                                              block_capacity=args.batch * pages_per_request + 8),

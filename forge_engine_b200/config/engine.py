@@ -47,7 +47,9 @@ class SchedulerConfig:
     ``block_size`` tokens per page, ``block_capacity`` pages in the pool,
     ``token_budget`` tokens per step over all requests, ``max_batch_size`` requests
     per step, ``max_requests`` admitted and unfinished at once, ``chunk_size`` the
-    most prompt tokens of one request in one step (None: only the budget limits it).
+    most prompt tokens of one request in one step (None: only the budget limits it),
+    ``lookahead`` lets steps of decoding requests only be launched one ahead of the
+    host's bookkeeping (their events then arrive one ``step()`` later).
     """
 
     max_requests: int = 16
@@ -56,6 +58,7 @@ class SchedulerConfig:
     block_size: int = 16
     block_capacity: int = 1024
     chunk_size: int | None = None
+    lookahead: bool = True
 
     def __post_init__(self) -> None:
         for name in ("max_requests", "max_batch_size", "token_budget", "block_size", "block_capacity"):

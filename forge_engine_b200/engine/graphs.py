@@ -99,9 +99,11 @@ class DecodeGraphs:
             self.pool = graph.pool()
         return _CapturedStep(graph, buffer, logits, native.LAUNCHES - before)
 
-    def run(self, entries) -> torch.Tensor:
+    def run(self, entries, device_tokens: tuple | None = None) -> torch.Tensor:
         """Replay the step for ``entries`` (one token each; pages already reserved).
-        Returns logits for the entries that want them, in entry order."""
+        Returns logits for the entries that want them, in entry order.  With
+        ``device_tokens = (tensor, rows)`` entry i's token is ``tensor[rows[i]]``, copied
+        on the device after the step's other integers have been uploaded."""
         bucket_entries = min(_bucket(len(entries)), _bucket(self.max_entries))
         widest = max(
             (len(self.cache.request(e.key).tables[g].pages) for e in entries for g in range(len(self.cache.groups))),
@@ -118,6 +120,12 @@ class DecodeGraphs:
         plan = self._plan(full, *key)
         assert len(plan.flat) == step.buffer.numel()
         step.upload(plan.flat)
+        if device_tokens is not None:
+            source, rows = device_tokens
+            begin, _ = plan.offsets["token_ids"]
+            if list(rows) != list(range(len(rows))) or source.numel() != len(rows):
+                source = source.index_select(0, torch.tensor(rows, dtype=torch.long, device=source.device))
+            step.buffer[begin : begin + len(entries)].copy_(source)
         step.graph.replay()
         native.LAUNCHES += step.launches
         if len(wanted) == len(entries):

@@ -107,8 +107,17 @@ class ModelRunner:
         self.cache.end_request(key)
 
     # -- the step ------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    @property
+    def supports_device_tokens(self) -> bool:
+        """Whether ``step`` can take a decode step's input tokens from a device tensor."""
+        return self.use_graphs
+
+    def step(self, entries: Sequence[StepEntry], device_tokens: tuple | None = None) -> torch.Tensor:
         """Run the entries' tokens as one batch from the cache earlier steps left.
+
+        ``device_tokens = (int32 tensor on the device, rows)`` replaces the entries' (single)
+        tokens by ``tensor[rows[i]]`` without a round trip through the host; only for steps
+        in which every entry brings one token, on a runner that replays captured steps.
 
         Returns 32-bit logits [number of wanted places, vocab] on the device, ordered by
         entry and by ``want``.  Pages are leased before anything runs; if they run out,
@@ -122,7 +131,7 @@ class ModelRunner:
         for entry in entries:
             if len(entry.tokens) < 1:
                 raise ValueError(f"request {entry.key!r} brings no tokens")
-            for token in entry.tokens:
+            for token in entry.tokens if device_tokens is None else ():
                 if not 0 <= int(token) < vocab:
                     raise ValueError(f"request {entry.key!r}: token id {token} is outside the vocabulary")
             request = self.cache.request(entry.key)
@@ -143,8 +152,10 @@ class ModelRunner:
             raise
         try:
             with torch.cuda.device(self.ctx.device):
+                if device_tokens is not None and not (self.use_graphs and all(len(e.tokens) == 1 for e in entries)):
+                    raise ValueError("device tokens need a replayed step of single tokens")
                 if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
-                    logits = self.graphs.run(entries)
+                    logits = self.graphs.run(entries, device_tokens)
                     n_tokens = len(entries)
                 else:
                     batch = build_batch(entries, self.cache, self.ctx.device)

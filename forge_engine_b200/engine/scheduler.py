@@ -86,6 +86,16 @@ class SchedulerSnapshot:
 
 
 @dataclass
+class _Inflight:
+    """A decode step whose sampled tokens have not been read back yet."""
+
+    requests: list          # row order of the step
+    tokens_device: object   # int32 [rows] on the device
+    tokens_host: object     # pinned host copy, valid once ``event`` has passed
+    event: object
+
+
+@dataclass
 class _Request:
     request_id: str
     prompt: list
@@ -133,6 +143,16 @@ class Scheduler:
         self._iteration = 0
         self._last_batch: tuple = ()
         self._rng = random.Random(seed)
+        # Decode steps can be launched one ahead: the next step takes its tokens from the
+        # sampler's output on the device while the host is still reading the last ones, so
+        # the GPU does not idle during the host's bookkeeping.  Needs a runner that replays
+        # captured steps and a sampler that can leave its result on the device.
+        self.lookahead = bool(
+            self.config.lookahead
+            and getattr(runner, "supports_device_tokens", False)
+            and hasattr(sampler, "sample_async")
+        )
+        self._inflight: _Inflight | None = None
 
     # -- admission -----------------------------------------------------------------
     def _max_portion(self) -> int:
@@ -226,6 +246,89 @@ class Scheduler:
         return selected
 
     def step(self) -> list:
+        """One scheduling iteration.  With look-ahead, a step of decoding requests only is
+        launched before the tokens of the step before it have been read; its events are
+        then those of the earlier step."""
+        if self._inflight is not None:
+            if all(r.status.terminal for r in self._inflight.requests):
+                self._inflight = None      # everything it decoded for has ended meanwhile
+            else:
+                return self._step_chained()
+        if self.lookahead:
+            self._admit()
+            decoders = self._all_decoding()
+            if decoders:
+                return self._launch_ahead(decoders, None)
+        return self._step_sync()
+
+    # -- look-ahead ------------------------------------------------------------------
+    def _all_decoding(self) -> list:
+        """The unfinished requests, if every one of them is decoding and they fit one step."""
+        if self._queue:
+            return []
+        live = [self._requests[rid] for rid in self._order if not self._requests[rid].status.terminal]
+        if not live or len(live) > min(self.config.max_batch_size, self.config.token_budget):
+            return []
+        if any(r.status is not RequestStatus.RUNNING for r in live):
+            return []
+        return live
+
+    def _launch_ahead(self, requests: list, previous: _Inflight | None) -> list:
+        """Launch one decode step for ``requests`` without waiting for its tokens.  With
+        ``previous`` the input tokens are that step's sampled ids, still on the device."""
+        self._iteration += 1
+        self._last_batch = tuple((r.request_id, 1) for r in requests)
+        extra = 0 if previous is None else 1     # tokens sampled but not yet counted on the host
+        try:
+            if previous is None:
+                entries = [StepEntry(r.request_id, [r.pending_token], [0]) for r in requests]
+                logits = self.runner.step(entries)
+            else:
+                rows = [previous.requests.index(r) for r in requests]
+                entries = [StepEntry(r.request_id, [0], [0]) for r in requests]
+                logits = self.runner.step(entries, device_tokens=(previous.tokens_device, rows))
+            device, host, event = self.sampler.sample_async(
+                logits,
+                [r.params for r in requests],
+                [r.seed for r in requests],
+                [len(r.output) + extra for r in requests],
+            )
+        except Exception as error:
+            events = []
+            for request in requests:
+                request.status = RequestStatus.FAILED
+                request.finish_reason = "error"
+                request.error = f"{type(error).__name__}: {error}"
+                self._cleanup(request)
+                events.append(StreamEvent(request.request_id, (), request.status))
+            self._inflight = None
+            self._drop_terminal()
+            return events
+        self._inflight = _Inflight(list(requests), device, host, event)
+        return []
+
+    def _step_chained(self) -> list:
+        """Launch the next decode step from the device tokens of the one in flight (if the
+        batch can go on unchanged), then read the earlier step's tokens and book them."""
+        previous = self._inflight
+        self._inflight = None
+        events: list[StreamEvent] = []
+        live = [r for r in previous.requests if not r.status.terminal]
+        # a request whose next token is its last by the length limit does not go on
+        survivors = [r for r in live if len(r.output) + 1 < r.params.max_new_tokens]
+        others = [self._requests[rid] for rid in self._order
+                  if not self._requests[rid].status.terminal and self._requests[rid] not in previous.requests]
+        if survivors and not self._queue and not others:
+            events.extend(self._launch_ahead(survivors, previous))
+        previous.event.synchronize()
+        tokens = previous.tokens_host.tolist()
+        for request, token in zip(previous.requests, tokens):
+            if not request.status.terminal:
+                events.extend(self._consume(request, int(token)))
+        self._drop_terminal()
+        return events
+
+    def _step_sync(self) -> list:
         """Admit, select, run one model step, sample, finish (src/forge_engine/scheduler.py:274-310)."""
         self._admit()
         selected = self._select()

@@ -21,9 +21,13 @@ def _to_signed64(value: int) -> int:
 
 
 class Sampler:
+    RING = 4   # pinned result buffers; one is reused four asynchronous calls later
+
     def __init__(self, device, status: torch.Tensor) -> None:
         self.device = torch.device(device)
         self.status = status
+        self._pinned: list = []
+        self._turn = 0
 
     def sample(
         self,
@@ -48,12 +52,27 @@ class Sampler:
         longs = torch.tensor(
             [[_to_signed64(s) for s in seeds], [_to_signed64(c) for c in counters]], dtype=torch.int64
         )
-        floats = floats.to(self.device, non_blocking=True)
-        top_k = top_k.to(self.device, non_blocking=True)
-        longs = longs.to(self.device, non_blocking=True)
+        floats = floats.pin_memory().to(self.device, non_blocking=True)
+        top_k = top_k.pin_memory().to(self.device, non_blocking=True)
+        longs = longs.pin_memory().to(self.device, non_blocking=True)
         native.sample(logits, out, self.status, temperature=floats[0], top_k=top_k, top_p=floats[1],
                       min_p=floats[2], seeds=longs[0], counters=longs[1])
         return out
 
     def sample_to_host(self, logits, params, seeds, counters) -> list:
         return self.sample(logits, params, seeds, counters).tolist()
+
+    def sample_async(self, logits, params, seeds, counters) -> tuple:
+        """Sample and start copying the ids to pinned host memory without waiting:
+        returns (ids on the device, pinned host tensor, event that marks the copy done)."""
+        device = self.sample(logits, params, seeds, counters)
+        rows = device.numel()
+        # pinned memory is allocated once and reused: allocating it stalls the device
+        if not self._pinned or self._pinned[0].numel() < rows:
+            self._pinned = [torch.empty(max(rows, 256), dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        host = self._pinned[self._turn % self.RING][:rows]
+        self._turn += 1
+        host.copy_(device, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return device, host, event

@@ -535,3 +535,47 @@ def test_graph_replay_equals_eager_steps(fe, dtype, tmp_path) -> None:
             torch.testing.assert_close(replayed, ref[pos_g], **bound(dtype, ref))
             if dtype == "float32":
                 assert torch.equal(eager, replayed)
+
+
+def test_lookahead_gives_the_same_tokens_as_synchronous_steps(fe, tmp_path) -> None:
+    """Decode steps launched one ahead (tokens fed on the device, events one step late)
+    against fully synchronous scheduling: same outputs, greedy and sampled, with requests
+    that stop on an end-of-sequence id in the middle and a late arrival."""
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine
+    from forge_engine_b200.sampling import SamplingParams
+
+    # many end-of-sequence ids, so that sampled requests do stop early
+    raw = dict(plain.TINY_B, eos_token_id=list(range(300, 384)))
+    cfg, weights = make_model_folder(tmp_path / "m", raw, 2)
+    prompts = [random_ids(300, n, 70 + n) for n in (5, 12, 3, 20)]
+    params = [SamplingParams(max_new_tokens=30), SamplingParams(temperature=1.0, seed=3, max_new_tokens=25),
+              SamplingParams(temperature=0.9, top_k=40, seed=9, max_new_tokens=12),
+              SamplingParams(temperature=1.2, seed=5, max_new_tokens=30)]
+    late_prompt = random_ids(300, 7, 99)
+    results = {}
+    for lookahead in (False, True):
+        engine = Engine.from_pretrained(
+            tmp_path / "m", engine_config=EngineConfig(dtype="float32"),
+            scheduler_config=SchedulerConfig(block_size=16, block_capacity=32, token_budget=64, max_batch_size=8,
+                                             lookahead=lookahead))
+        assert engine.scheduler.lookahead == lookahead
+        ids = [engine.submit(p, sampling_params=sp) for p, sp in zip(prompts, params)]
+        steps = 0
+        late = None
+        while not engine.scheduler.idle:
+            engine.step()
+            steps += 1
+            if steps == 6:
+                late = engine.submit(late_prompt, sampling_params=SamplingParams(max_new_tokens=9))
+        views = [engine.scheduler.request(r) for r in ids + [late]]
+        results[lookahead] = [(v.output_tokens, v.finish_reason) for v in views]
+        snap = engine.scheduler.snapshot()
+        assert snap.allocated_blocks == (0,) and snap.reserved_blocks == (0,)
+        engine.runner.check_status()
+    assert results[True] == results[False]
+    reasons = [reason for _, reason in results[True]]
+    assert "stop" in reasons and "length" in reasons      # both ways of finishing were exercised
+    # the greedy request equals the plain implementation's greedy continuation up to its stop
+    greedy_tokens = list(results[True][0][0])
+    assert greedy_tokens == plain.greedy_generate(prompts[0], len(greedy_tokens), weights, plain.PlainConfig.from_dict(raw))
