@@ -70,28 +70,32 @@ class DecoderModel:
         return needs, shares
 
     def weight_bytes(self) -> int:
-        """Bytes of every distinct weight tensor a step reads once."""
-        seen, total = set(), 0
+        """Bytes of every distinct weight tensor a step reads once (tied tensors count once)."""
+        seen: dict[int, int] = {}
+        visited: set[int] = set()
 
         def visit(obj) -> None:
-            nonlocal total
             if isinstance(obj, torch.Tensor):
-                if obj.data_ptr() not in seen:
-                    seen.add(obj.data_ptr())
-                    total += obj.numel() * obj.element_size()
-            elif isinstance(obj, Linear):
-                visit(obj.weight)
+                if obj.is_floating_point():
+                    seen[obj.data_ptr()] = obj.numel() * obj.element_size()
+                return
+            if id(obj) in visited or isinstance(obj, (BuildContext, ModelSpec, str, int, float, type(None))):
+                return
+            visited.add(id(obj))
+            if isinstance(obj, (list, tuple)):
+                for item in obj:
+                    visit(item)
+            elif isinstance(obj, dict):
+                for item in obj.values():
+                    visit(item)
             elif hasattr(obj, "__dict__"):
-                for value in vars(obj).values():
-                    if isinstance(value, (torch.Tensor, Linear)) or hasattr(value, "__dict__"):
-                        if not isinstance(value, (BuildContext, type)) and value is not self.spec:
-                            visit(value)
+                for item in vars(obj).values():
+                    visit(item)
 
-        for block in self.blocks:
-            visit(block)
+        visit(self.blocks)
         visit(self.final_norm)
         visit(self.head)
-        return total
+        return sum(seen.values())
 
     # -- one step ------------------------------------------------------------------
     def forward(self, batch, cache) -> torch.Tensor:

@@ -579,3 +579,38 @@ def test_lookahead_gives_the_same_tokens_as_synchronous_steps(fe, tmp_path) -> N
     # the greedy request equals the plain implementation's greedy continuation up to its stop
     greedy_tokens = list(results[True][0][0])
     assert greedy_tokens == plain.greedy_generate(prompts[0], len(greedy_tokens), weights, plain.PlainConfig.from_dict(raw))
+
+
+def test_benchmark_layer_shapes_in_32_bit_and_bfloat16(fe, tmp_path) -> None:
+    """Two layers with the layer sizes of the 4B benchmark model (hidden 2560, 32/8 heads of
+    128, intermediate 9728, theta 5e6) and a vocabulary that is no multiple of 128: the
+    32-bit engine against the plain implementation, whole and cut, and the bfloat16 engine
+    (tcgen05 products, tensor-core attention, replayed decode steps) against the same."""
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+
+    raw = dict(plain.TINY_A, vocab_size=5003, hidden_size=2560, intermediate_size=9728, num_hidden_layers=2,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=5e6, rms_norm_eps=1e-6,
+               tie_word_embeddings=True, eos_token_id=None)
+    cfg, weights = make_model_folder(tmp_path / "m", raw, 11)
+    ids = random_ids(cfg.vocab_size, 150, 4)
+    ref = plain.forward_logits(ids, weights, cfg)
+    for dtype in ("float32", "bfloat16"):
+        runner = ModelRunner.from_folder(tmp_path / "m", dtype=dtype, page_size=16, num_pages=40, max_requests=4)
+        runner.begin("whole")
+        whole = runner.step([StepEntry("whole", ids, range(len(ids)))]).cpu()
+        runner.end("whole")
+        runner.begin("cut")
+        rows = [runner.step([StepEntry("cut", ids[:97], range(97))]).cpu(),
+                runner.step([StepEntry("cut", ids[97:118], range(21))]).cpu()]
+        rows += [runner.step([StepEntry("cut", [t], [0])]).cpu() for t in ids[118:]]
+        cut = torch.cat(rows)
+        runner.end("cut")
+        runner.check_status()
+        if dtype == "float32":
+            torch.testing.assert_close(whole, ref, atol=1e-4, rtol=1e-5)
+            torch.testing.assert_close(cut, ref, atol=1e-4, rtol=1e-5)
+        else:
+            for got in (whole, cut):
+                torch.testing.assert_close(got, ref, **bound(dtype, ref))
+                tv = 0.5 * (torch.softmax(got.double(), -1) - torch.softmax(ref.double(), -1)).abs().sum(-1).max()
+                assert float(tv) < 0.02
