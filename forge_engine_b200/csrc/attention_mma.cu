@@ -878,20 +878,26 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 // Tensor map of one cache matrix seen as [pages * kv heads * page_size rows, D columns]:
 // boxes of page_size rows x 64 columns, 128-byte swizzle, zeros outside.  Maps are kept
 // per (pointer, rows, page size): a model has two per attention layer.
+EncodeTiledFn g_encode_tiled = nullptr;
+
+bool ensure_encode() {
+  if (g_encode_tiled == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return g_encode_tiled != nullptr;
+}
+
 const CUtensorMap* cache_map(const void* base, int rows, int page_size) {
   static std::map<std::tuple<const void*, int, int>, CUtensorMap> maps;
-  static EncodeTiledFn encode = nullptr;
   const auto key = std::make_tuple(base, rows, page_size);
   auto found = maps.find(key);
   if (found != maps.end()) return &found->second;
-  if (encode == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
-        result != cudaDriverEntryPointSuccess)
-      return nullptr;
-    encode = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+  if (!ensure_encode()) return nullptr;
+  EncodeTiledFn encode = g_encode_tiled;
   CUtensorMap map;
   cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)D * 2};
@@ -907,6 +913,8 @@ const CUtensorMap* cache_map(const void* base, int rows, int page_size) {
 
 }  // namespace
 
+#include "attention_tc5.cuh"
+
 // Workspace sizes (in floats) the decode path needs for `entries` and `num_splits`.
 FE_EXPORT long long SYM(fe_attn_workspace_floats_d)(int entries, int num_kv_heads, int num_splits) {
   return (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
@@ -921,8 +929,8 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
                                       const void* v_cache, const int* block_table, int max_pages,
                                       int page_size, int num_pages, int num_kv_heads, int groups,
                                       const int* cu_tokens, const int* starts, int entries, int max_new,
-                                      int window, float scale, int mode, int num_splits, float* workspace,
-                                      unsigned* counters, int* status, cudaStream_t stream) {
+                                      int total_tokens, int window, float scale, int mode, int num_splits,
+                                      float* workspace, unsigned* counters, int* status, cudaStream_t stream) {
   if (entries <= 0) return 0;
   if (groups < 1 || groups > DEC_ROWS || num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return FE_ERR_BAD_SHAPE;
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
@@ -953,9 +961,30 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
     const int max_rows = max_new * groups;
     if (max_rows > decode_rows) {
       p.row_lo = decode_rows; p.row_hi = 0x7fffffff;
-      dim3 grid((max_rows + BM - 1) / BM, entries, num_kv_heads);
-      const int rc = fe_launch_dependent(attn_prefill_kernel, grid, dim3(THREADS), PREFILL_SMEM, stream, p);
-      if (rc) return rc;
+      // tcgen05 form where its shapes hold; FORGE_ENGINE_PREFILL_MMA=1 keeps the mma.sync kernel
+      static const bool force_mma = getenv("FORGE_ENGINE_PREFILL_MMA") != nullptr && getenv("FORGE_ENGINE_PREFILL_MMA")[0] == '1';
+      const bool tc5_ok = !force_mma && (D == 128 || D == 64) && (TC5_ROWS % groups) == 0 && page_size <= TC5_KEYS &&
+                          (TC5_KEYS % page_size) == 0 && ensure_encode();
+      const CUtensorMap* mk = tc5_ok ? cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
+      const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
+      CUtensorMap mq;
+      if (mk && mv && make_query_map(&mq, q, q_stride, total_tokens, num_kv_heads * groups, groups) == 0) {
+        static bool tc5_configured = false;
+        if (!tc5_configured) {
+          const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     (int)TC5_SMEM);
+          if (e != cudaSuccess) return (int)e;
+          tc5_configured = true;
+        }
+        dim3 grid((max_rows + TC5_ROWS - 1) / TC5_ROWS, entries, num_kv_heads);
+        const int rc = fe_launch_dependent(attn_prefill_tc5_kernel, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, *mk,
+                                           *mv, p);
+        if (rc) return rc;
+      } else {
+        dim3 grid((max_rows + BM - 1) / BM, entries, num_kv_heads);
+        const int rc = fe_launch_dependent(attn_prefill_kernel, grid, dim3(THREADS), PREFILL_SMEM, stream, p);
+        if (rc) return rc;
+      }
     }
   }
   if (use_decode) {

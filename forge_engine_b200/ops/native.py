@@ -86,7 +86,7 @@ def attention_lib(head_dim: int):
             raise CUDAUnavailableError(f"cannot load {path}: {error}") from error
         fn = getattr(handle, f"fe_attention_mma_d{head_dim}")
         p, i, f = c_void_p, c_int, c_float
-        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, f, i, i, p, p, p, p]
+        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, i, f, i, i, p, p, p, p]
         fn.restype = c_int
         _attention_libs[head_dim] = fn
     return fn
@@ -314,7 +314,7 @@ def attention_mma(
         attention_lib(head_dim)(
             ptr(q), int(q_stride), ptr(out), ptr(k_cache), ptr(v_cache), ptr(block_table),
             block_table.shape[1], page_size, num_pages, nkv, groups, ptr(cu_tokens), ptr(starts),
-            entries, int(max_new), int(window or 0), float(scale), mode, int(num_splits),
+            entries, int(max_new), int(q.shape[0]), int(window or 0), float(scale), mode, int(num_splits),
             ptr(workspace), ptr(counters), ptr(status), stream(),
         ),
         "attention_mma",
