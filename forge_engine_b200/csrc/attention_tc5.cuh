@@ -16,8 +16,9 @@
 //            and sum in 32-bit, writes P; rescales O only when the maximum has grown by
 //            more than 2^8 (the final division by the sum makes this exact); at the end
 //            normalises O and stores it
-//   Two such blocks fit on an SM (96 KB shared memory, 256 tensor-memory columns each), so
-//   one block's softmax overlaps the other's products.
+//   Scores and probabilities are double-buffered in tensor memory: the scores of tile t+1
+//   (and t+2) are computed while the softmax warps still work on tile t, so the tensor
+//   core never waits for the softmax and the softmax only for its own arithmetic.
 #pragma once
 
 namespace {
@@ -25,16 +26,16 @@ namespace {
 constexpr int TC5_ROWS = 128;       // query rows per block
 constexpr int TC5_KEYS = 64;        // keys per tile
 constexpr int TC5_THREADS = 192;
-constexpr int TC5_KV_STAGES = 2;
-constexpr int TC5_TMEM_COLS = 256;
-constexpr int TC5_COL_S = 0;        // 64 columns of 32-bit scores
-constexpr int TC5_COL_P = 64;       // 32 columns holding 64 bfloat16 probabilities
-constexpr int TC5_COL_O = 128;      // D columns of 32-bit output accumulators (D <= 128)
+constexpr int TC5_KV_STAGES = 4;
+constexpr int TC5_TMEM_COLS = 512;
+constexpr int TC5_COL_S = 0;        // 2 x 64 columns of 32-bit scores
+constexpr int TC5_COL_P = 128;      // 2 x 32 columns holding 64 bfloat16 probabilities each
+constexpr int TC5_COL_O = 256;      // D columns of 32-bit output accumulators (D <= 128)
 constexpr float TC5_RESCALE_STEP = 8.f;   // in log2 units
 
 constexpr int TC5_Q_BYTES = TC5_ROWS * D * 2;
 constexpr int TC5_KV_BYTES = TC5_KEYS * D * 2;   // one matrix of one stage
-constexpr size_t TC5_SMEM = (size_t)TC5_Q_BYTES + (size_t)2 * TC5_KV_STAGES * TC5_KV_BYTES + 16 * 8 + 64 + 1024;
+constexpr size_t TC5_SMEM = (size_t)TC5_Q_BYTES + (size_t)2 * TC5_KV_STAGES * TC5_KV_BYTES + 24 * 8 + 64 + 1024;
 
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
@@ -85,6 +86,13 @@ __device__ __forceinline__ void tc5_mma_ts(unsigned tmem_d, unsigned tmem_a, uin
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc) : "memory");
 }
+// 2^x by the special-function unit's single instruction (the bfloat16 path rounds the
+// result to 8 bits anyway); exp2f() costs several times as many instructions.
+__device__ __forceinline__ float tc5_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void tc5_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
@@ -127,9 +135,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;                 // [stages]
   uint64_t* kv_empty = kv_full + TC5_KV_STAGES; // [stages]
-  uint64_t* s_full = kv_empty + TC5_KV_STAGES;
-  uint64_t* p_full = s_full + 1;
-  uint64_t* o_full = p_full + 1;
+  uint64_t* s_full = kv_empty + TC5_KV_STAGES;   // [2]
+  uint64_t* p_full = s_full + 2;                 // [2]
+  uint64_t* pv_done = p_full + 2;                // completes once per value product
+  uint64_t* o_full = pv_done + 1;
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -156,8 +165,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < TC5_KV_STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
+    for (int b = 0; b < 2; ++b) { mbar_init(s_full + b, 1); mbar_init(p_full + b, 4); }
+    mbar_init(pv_done, 1);
     mbar_init(o_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,30 +233,38 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const unsigned idesc_qk = tc5_idesc(TC5_ROWS, TC5_KEYS, false);
       const unsigned idesc_pv = tc5_idesc(TC5_ROWS, D, true);
       bool ok = mbar_wait(q_full, 0, abort_flag);
-      for (int i = 0; i < my_tiles && ok; ++i) {
-        const int s = i % TC5_KV_STAGES;
-        ok = mbar_wait(kv_full + s, (i / TC5_KV_STAGES) & 1, abort_flag);
-        if (!ok) break;
+      // scores of tile t into buffer t % 2
+      auto issue_scores = [&](int t) -> bool {
+        const int s = t % TC5_KV_STAGES;
+        if (!mbar_wait(kv_full + s, (t / TC5_KV_STAGES) & 1, abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // S = Q K^T : D / 16 steps of k = 16 (32 bytes along the swizzled row, 4 per 64-column block)
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          // k = 16 is 32 bytes along the swizzled row, 4 steps per 64-column block
           const uint64_t da = tc5_desc_kmajor(q_tile + (kk >> 2) * (TC5_ROWS * 128)) + (uint64_t)((kk & 3) * 2);
           const uint64_t db = tc5_desc_kmajor(k_tiles + s * TC5_KV_BYTES + (kk >> 2) * (TC5_KEYS * 128)) + (uint64_t)((kk & 3) * 2);
-          tc5_mma_ss(tmem_base + TC5_COL_S, da, db, idesc_qk, kk != 0 ? 1u : 0u);
+          tc5_mma_ss(tmem_base + TC5_COL_S + (t & 1) * TC5_KEYS, da, db, idesc_qk, kk != 0 ? 1u : 0u);
         }
-        tc5_commit(s_full);
-        // wait for the probabilities of this tile
-        ok = mbar_wait(p_full, i & 1, abort_flag);
+        tc5_commit(s_full + (t & 1));
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      if (ok && my_tiles > 1) ok = issue_scores(1);
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int s = i % TC5_KV_STAGES;
+        ok = mbar_wait(p_full + (i & 1), (i >> 1) & 1, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // O += P V : 4 steps of 16 keys; V is MN-major, 16 keys = 2048 bytes further down
 #pragma unroll
         for (int kk = 0; kk < TC5_KEYS / 16; ++kk) {
           const uint64_t db = tc5_desc_mnmajor(v_tiles + s * TC5_KV_BYTES + kk * 2048, TC5_KEYS * 128);
-          tc5_mma_ts(tmem_base + TC5_COL_O, tmem_base + TC5_COL_P + kk * 8, db, idesc_pv, (i | kk) != 0 ? 1u : 0u);
+          tc5_mma_ts(tmem_base + TC5_COL_O, tmem_base + TC5_COL_P + (i & 1) * (TC5_KEYS / 2) + kk * 8, db, idesc_pv,
+                     (i | kk) != 0 ? 1u : 0u);
         }
         tc5_commit(kv_empty + s);     // the stage may be refilled when these products are done
+        tc5_commit(pv_done);
+        if (i + 2 < my_tiles) ok = issue_scores(i + 2);
       }
       tc5_commit(o_full);
     }
@@ -263,13 +280,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < my_tiles && ok; ++i) {
-      ok = mbar_wait(s_full, i & 1, abort_flag);
+      ok = mbar_wait(s_full + (i & 1), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int key0 = (tile_begin + i) * TC5_KEYS;
       float s0[32], s1[32];
-      tc5_ld32(lane_addr + TC5_COL_S, s0);
-      tc5_ld32(lane_addr + TC5_COL_S + 32, s1);
+      tc5_ld32(lane_addr + TC5_COL_S + (i & 1) * TC5_KEYS, s0);
+      tc5_ld32(lane_addr + TC5_COL_S + (i & 1) * TC5_KEYS + 32, s1);
       // every key of the tile visible to every row of the block?
       const bool clear = key0 + TC5_KEYS - 1 <= pos_first && key0 + TC5_KEYS <= key_end && row0 + TC5_ROWS <= rows_total &&
                          (p.window <= 0 || pos_last - key0 < p.window);
@@ -298,17 +315,19 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       unsigned packed[32];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const float a0 = exp2f(s0[2 * j] - base), a1 = exp2f(s0[2 * j + 1] - base);
-        const float b0 = exp2f(s1[2 * j] - base), b1 = exp2f(s1[2 * j + 1] - base);
+        const float a0 = tc5_exp2(s0[2 * j] - base), a1 = tc5_exp2(s0[2 * j + 1] - base);
+        const float b0 = tc5_exp2(s1[2 * j] - base), b1 = tc5_exp2(s1[2 * j + 1] - base);
         sum += (a0 + a1) + (b0 + b1);
         packed[j] = pack_bf16(a0, a1);
         packed[16 + j] = pack_bf16(b0, b1);
       }
       l = l * corr + sum;
-      // s_full of this tile implies the value product of the tile before has finished, so
-      // P and O may be touched now
-      tc5_st32(lane_addr + TC5_COL_P, packed);
+      // the scores of this tile were issued after the value product of tile i - 2, which
+      // read this P buffer: it is free.  O is only touched once product i - 1 has finished.
+      tc5_st32(lane_addr + TC5_COL_P + (i & 1) * (TC5_KEYS / 2), packed);
       if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+        if (!mbar_wait(pv_done, (i - 1) & 1, abort_flag)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           float o[32];
@@ -322,7 +341,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full + (i & 1));
     }
     // final: normalise and store this row
     if (ok) ok = mbar_wait(o_full, 0, abort_flag);
