@@ -964,7 +964,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
       // tcgen05 form where its shapes hold; FORGE_ENGINE_PREFILL_MMA=1 keeps the mma.sync kernel
       static const bool force_mma = getenv("FORGE_ENGINE_PREFILL_MMA") != nullptr && getenv("FORGE_ENGINE_PREFILL_MMA")[0] == '1';
       const bool tc5_ok = !force_mma && (D == 128 || D == 64) && (TC5_ROWS % groups) == 0 && page_size <= TC5_KEYS &&
-                          (TC5_KEYS % page_size) == 0 && ensure_encode();
+                          page_size * 32 >= TC5_KEYS && (TC5_KEYS % page_size) == 0 && scale > 0.f && ensure_encode();
       const CUtensorMap* mk = tc5_ok ? cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
       const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
       CUtensorMap mq;
@@ -976,7 +976,9 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
           if (e != cudaSuccess) return (int)e;
           tc5_configured = true;
         }
-        dim3 grid((max_rows + TC5_ROWS - 1) / TC5_ROWS, entries, num_kv_heads);
+        const int query_blocks = (max_rows + TC5_BLOCK_ROWS - 1) / TC5_BLOCK_ROWS;
+        if (query_blocks > 65535) return FE_ERR_TOO_LARGE;
+        dim3 grid(num_kv_heads, entries, query_blocks);
         const int rc = fe_launch_dependent(attn_prefill_tc5_kernel, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, *mk,
                                            *mv, p);
         if (rc) return rc;

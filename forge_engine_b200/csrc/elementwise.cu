@@ -96,15 +96,89 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __res
   }
 }
 
+// Rows whose length is a multiple of 4 and at most 4 * 4 * 1024: a thread keeps up to PER
+// groups of four neighbouring elements (16-byte loads of the residual), same arithmetic.
+template <typename TU, typename TO, int PER>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TU* __restrict__ update,
+                                       const float* __restrict__ weight, TO* __restrict__ out,
+                                       const int* __restrict__ row_map, int size, float eps,
+                                       int write_residual) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = row_map ? row_map[r] : r;
+  float* res = residual + (size_t)src * size;
+  const TU* upd = update ? update + (size_t)src * size : nullptr;
+  TO* dst = out + (size_t)r * size;
+  const int groups = size >> 2;
+  float x[PER][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int g = threadIdx.x + j * blockDim.x;
+    if (g < groups) {
+      load4(res + 4 * g, x[j]);
+      if (upd) {
+        float u[4];
+        load4(upd + 4 * g, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[j][e] += u[e];
+      }
+      if (write_residual) store4(res + 4 * g, x[j]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += x[j][e] * x[j][e];
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, scratch) / (float)size + eps);
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int g = threadIdx.x + j * blockDim.x;
+    if (g < groups) {
+      float w[4], y[4];
+      load4(weight + 4 * g, w);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[e] = x[j][e] * inv * w[e];
+      store4(dst + 4 * g, y);
+    }
+  }
+}
+
 FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dtype,
                              const float* weight, void* out, int out_dtype, const int* row_map,
                              int rows, int size, float eps, int write_residual,
                              cudaStream_t stream) {
   if (rows <= 0) return 0;
+  int rc = 0;
+  const int update_bytes = update_dtype == FE_DTYPE_F32 ? 16 : 8, out_bytes = out_dtype == FE_DTYPE_F32 ? 16 : 8;
+  if ((size % 4) == 0 && size <= 16384 && ((uintptr_t)residual % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
+      ((uintptr_t)update % update_bytes) == 0 && ((uintptr_t)out % out_bytes) == 0) {
+    const int groups = size / 4;
+    const int per = groups <= 1024 ? 1 : groups <= 2048 ? 2 : 4;
+    const int vthreads = (((groups + per - 1) / per) + 31) / 32 * 32;
+#define LAUNCH_VEC(TU, TO)                                                                                        \
+    do {                                                                                                          \
+      if (per == 1)                                                                                               \
+        rc = fe_launch_dependent(add_rmsnorm_vec_kernel<TU, TO, 1>, dim3(rows), dim3(vthreads), 0, stream, residual, \
+            (const TU*)update, weight, (TO*)out, row_map, size, eps, write_residual);                             \
+      else if (per == 2)                                                                                          \
+        rc = fe_launch_dependent(add_rmsnorm_vec_kernel<TU, TO, 2>, dim3(rows), dim3(vthreads), 0, stream, residual, \
+            (const TU*)update, weight, (TO*)out, row_map, size, eps, write_residual);                             \
+      else                                                                                                        \
+        rc = fe_launch_dependent(add_rmsnorm_vec_kernel<TU, TO, 4>, dim3(rows), dim3(vthreads), 0, stream, residual, \
+            (const TU*)update, weight, (TO*)out, row_map, size, eps, write_residual);                             \
+    } while (0)
+    if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH_VEC(float, float);
+    else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH_VEC(bf16, bf16);
+    else if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) LAUNCH_VEC(float, bf16);
+    else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_F32) LAUNCH_VEC(bf16, float);
+    else return FE_ERR_BAD_DTYPE;
+#undef LAUNCH_VEC
+    return rc ? rc : fe_last_error();
+  }
   int threads = 32;
   while (threads < 512 && threads * 4 < size) threads <<= 1;
   const int per = (size + threads - 1) / threads;
-  int rc = 0;
 #define LAUNCH(TU, TO)                                                                               \
   do {                                                                                               \
     if (per <= 4)                                                                                    \

@@ -95,6 +95,99 @@ __global__ void qk_rope_cache_kernel(T* __restrict__ qkv, const float* __restric
   }
 }
 
+// bfloat16, the whole head rotated, D a multiple of 64 up to 256: a group of D/8 lanes takes
+// one head, every lane four neighbouring elements of the first half and their partners in
+// the second half (two 8-byte loads, kept in registers between the norm and the rotation).
+// Cosine and sine depend on the token and the pair only: a lane computes its four once and
+// uses them for every head it meets.  Same arithmetic, element by element, as the kernel
+// above.
+template <int D>
+__global__ void qk_rope_cache_vec_kernel(bf16* __restrict__ qkv, const float* __restrict__ q_weight,
+                                         const float* __restrict__ k_weight, float eps,
+                                         const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                         const int* __restrict__ token_entry, PagedKV cache, int num_q_heads,
+                                         int write_kv, int* status) {
+  constexpr int LANES = D / 8;            // lanes per head
+  constexpr int HEADS = 32 / LANES;       // heads a warp takes at a time
+  constexpr int HALF = D / 2;
+  pdl_trigger();
+  pdl_wait();
+  const int token = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LANES, l = lane - sub * LANES;
+  const int warps = (blockDim.x >> 5) * gridDim.y;
+  const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int nkv = cache.num_kv_heads;
+  const int heads_total = num_q_heads + 2 * nkv;
+  const int pos = positions[token];
+  const int entry = token_entry[token];
+
+  int page = -1, slot = 0;
+  if (write_kv) {
+    const int logical = pos / cache.page_size;
+    slot = pos - logical * cache.page_size;
+    if (pos < 0 || logical >= cache.max_pages) {
+      if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, FE_STATUS_BAD_POSITION);
+    } else {
+      page = cache.block_table[(size_t)entry * cache.max_pages + logical];
+      if (page < 0 || page >= cache.num_pages) {
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, FE_STATUS_BAD_PAGE);
+        page = -1;
+      }
+    }
+  }
+
+  const int j0 = 4 * l;                   // this lane's pairs: (j0 + e, j0 + e + HALF)
+  float cs[4], sn[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    cs[e] = 1.f; sn[e] = 0.f;
+    if (inv_freq) {
+      const float angle = (float)pos * inv_freq[j0 + e];
+      cs[e] = cosf(angle);
+      sn[e] = sinf(angle);
+    }
+  }
+  unsigned group_mask = 0xffffffffu;
+  if constexpr (LANES < 32) group_mask = ((1u << LANES) - 1u) << (sub * LANES);
+
+  for (int head = warp * HEADS + sub; head < heads_total; head += warps * HEADS) {
+    bf16* x = qkv + (size_t)token * heads_total * D + (size_t)head * D;
+    const bool is_q = head < num_q_heads;
+    const bool is_k = !is_q && head < num_q_heads + nkv;
+    if (!is_q && (!write_kv || page < 0)) continue;
+    bf16* dst = x;  // q is rewritten in place
+    if (!is_q) {
+      const int kvh = is_k ? head - num_q_heads : head - num_q_heads - nkv;
+      dst = (bf16*)(is_k ? cache.k : cache.v) + kv_offset(cache, page, kvh, slot);
+    }
+    float a[4], b[4];
+    load4(x + j0, a);
+    load4(x + HALF + j0, b);
+    if (is_q || is_k) {
+      const float* w = is_q ? q_weight : k_weight;
+      float inv = 1.f;
+      if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+#pragma unroll
+        for (int offset = LANES / 2; offset > 0; offset >>= 1) ss += __shfl_xor_sync(group_mask, ss, offset);
+        inv = rsqrtf(ss / (float)D + eps);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float u = a[e] * inv, v = b[e] * inv;
+        if (w) { u *= w[j0 + e]; v *= w[j0 + e + HALF]; }
+        a[e] = u * cs[e] - v * sn[e];
+        b[e] = v * cs[e] + u * sn[e];
+      }
+    }
+    store4(dst + j0, a);
+    store4(dst + HALF + j0, b);
+  }
+}
+
 FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, const float* k_weight,
                                float eps, const float* inv_freq, int rotary_dim,
                                const int* positions, const int* token_entry, void* k_cache,
@@ -114,6 +207,24 @@ FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, cons
   const int blocks_y = (warps_needed + warps - 1) / warps;
   if (blocks_y > 65535) return FE_ERR_TOO_LARGE;
   dim3 grid(n_tokens, blocks_y);
+  const bool vec = dtype == FE_DTYPE_BF16 && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+                   (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) & 7) == 0;
+  if (vec) {
+    // a warp takes 32 / (D / 8) heads at a time
+    const int at_a_time = 256 / head_dim;
+    const int slots = (heads_total + at_a_time - 1) / at_a_time;
+    per_warp = n_tokens >= 512 ? 4 : 1;
+    const int need = (slots + per_warp - 1) / per_warp;
+    const int w = need < 4 ? need : 4;
+    dim3 vgrid(n_tokens, (need + w - 1) / w);
+#define LAUNCH_VEC(DIM)                                                                                         \
+    return fe_launch_dependent(qk_rope_cache_vec_kernel<DIM>, vgrid, dim3(w * 32), 0, stream, (bf16*)qkv, q_weight, \
+                               k_weight, eps, inv_freq, positions, token_entry, cache, num_q_heads, write_kv, status)
+    if (head_dim == 64) LAUNCH_VEC(64);
+    if (head_dim == 128) LAUNCH_VEC(128);
+    LAUNCH_VEC(256);
+#undef LAUNCH_VEC
+  }
   if (dtype == FE_DTYPE_F32)
     return fe_launch_dependent(qk_rope_cache_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)qkv, q_weight, k_weight,
         eps, inv_freq, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
