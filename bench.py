@@ -211,6 +211,8 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1/64, prefill and e2e")
     parser.add_argument("--prefill-only", action="store_true",
                         help="time only the 2,048-token prefill (small cases for profiling)")
+    parser.add_argument("--kernel-times", action="store_true",
+                        help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()
     if args.impl == "reference":
         if args.gpus != 1:
@@ -308,11 +310,50 @@ def main() -> int:
         return {"value": round(CONTEXT / (ms_prefill / 1e3), 1), "tokens": CONTEXT, "ms": round(ms_prefill, 3),
                 "frac": round(flops / (ms_prefill / 1e3) / (bf16_tflops * 1e12), 4), "flops": flops}
 
+    def kernel_times(step) -> None:
+        """Device time of the kernels of one call of ``step`` (CUPTI through torch.profiler;
+        shares for reading, never a bench value)."""
+        from torch.profiler import ProfilerActivity, profile
+
+        step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        rows = {}
+        for event in prof.events():
+            if event.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in event.name:
+                count, total = rows.get(event.name, (0, 0.0))
+                rows[event.name] = (count + 1, total + event.time_range.end - event.time_range.start)
+        whole = sum(total for _, total in rows.values())
+        print(f"# kernels of one step: {whole:.0f} us summed over {sum(c for c, _ in rows.values())} launches")
+        for name, (count, total) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+            print(f"# {total:9.1f} us {100 * total / whole:5.1f}%  x{count:<4d} {total / count:7.1f} us each  {name[:90]}")
+
     if args.prefill_only:
-        print(json.dumps({"prefill": prefill_run(max(1, args.steps)), "layers": layers, "impl": "ours"}))
+        record = {"prefill": prefill_run(max(1, args.steps)), "layers": layers, "impl": "ours"}
+        if args.kernel_times:
+            prompt = torch.randint(0, raw["vocab_size"], (CONTEXT,), generator=gen).tolist()
+
+            def one_prefill():
+                runner.begin("kt")
+                runner.step([StepEntry("kt", prompt, [CONTEXT - 1])])
+                runner.end("kt")
+
+            kernel_times(one_prefill)
+        print(json.dumps(record))
         return 0
 
     ms_step, clocks, launches = decode_run(args.batch, args.steps, args.warmup)
+    if args.kernel_times:
+        keys = [f"kt{i}" for i in range(args.batch)]
+        for key in keys:
+            runner.begin(key)
+            runner.cache.reserve(key, CONTEXT)
+            runner.cache.advance(key, CONTEXT)
+        kernel_times(lambda: runner.step([StepEntry(k, [7], [0]) for k in keys]))
+        for key in keys:
+            runner.end(key)
     value = args.batch / (ms_step / 1e3)
     step_bytes = weight_bytes + args.batch * (CONTEXT + args.warmup + args.steps / 2) * kv_bytes_per_token
     achieved = step_bytes / (ms_step / 1e3) / 1e9
