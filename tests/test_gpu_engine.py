@@ -489,6 +489,182 @@ def test_toy_architecture_registers_builds_and_steps(fe, tmp_path) -> None:
     runner.cache.check_consistency()
 
 
+# ---------------------------------------------------------------------------
+# more toy parts defined here: a feed-forward with routing and another position encoding
+# ---------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class ToyRoutedSpec:
+    hidden_size: int
+    inter: int
+    experts: int
+    kind: str = "toy_routed_ffn"
+
+
+@dataclass(frozen=True)
+class ToyScaleSpec:
+    q_rate: float
+    k_rate: float
+    kind: str = "toy_scale_position"
+
+
+def register_toy_routed():
+    from forge_engine_b200.config import (Architecture, AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NormSpec,
+                                          RotarySpec, RunSpec, register_architecture)
+    from forge_engine_b200.parts import FeedForward, PositionEncoding, WeightInfo, register_part
+
+    class ToyRoutedFFN(FeedForward):
+        """Router logits in 32-bit, the best expert per token, its output weighted by the
+        expert's softmax probability: y = p_e * relu(x W1_e^T) W2_e^T."""
+
+        def __init__(self, spec, weights, ctx):
+            self.spec, self.dtype = spec, ctx.dtype
+            self.router = weights["router.weight"].float()
+            self.w1 = [weights[f"experts.{e}.w1.weight"].float() for e in range(spec.experts)]
+            self.w2 = [weights[f"experts.{e}.w2.weight"].float() for e in range(spec.experts)]
+
+        @classmethod
+        def weight_shapes(cls, spec):
+            shapes = {"router.weight": WeightInfo((spec.experts, spec.hidden_size))}
+            for e in range(spec.experts):
+                shapes[f"experts.{e}.w1.weight"] = WeightInfo((spec.inter, spec.hidden_size))
+                shapes[f"experts.{e}.w2.weight"] = WeightInfo((spec.hidden_size, spec.inter))
+            return shapes
+
+        def forward(self, x):
+            x = x.float()
+            prob = torch.softmax(x @ self.router.t(), -1)
+            best = prob.argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(self.spec.experts):
+                rows = (best == e).nonzero().flatten()
+                if rows.numel():
+                    y = torch.relu(x[rows] @ self.w1[e].t()) @ self.w2[e].t()
+                    out[rows] = prob[rows, e : e + 1] * y
+            return out.to(self.dtype)
+
+    class ToyScalePosition(PositionEncoding):
+        """Queries grow and keys shrink with their position: q *= 1 + q_rate * pos,
+        k /= 1 + k_rate * pos (no rotation)."""
+
+        def __init__(self, spec, weights, ctx):
+            self.spec = spec
+
+        @classmethod
+        def weight_shapes(cls, spec):
+            return {}
+
+        def apply(self, qkv, num_q_heads, num_kv_heads, head_dim, batch) -> None:
+            pos = batch.positions.to(torch.float32).unsqueeze(1)
+            q_end, k_end = num_q_heads * head_dim, (num_q_heads + num_kv_heads) * head_dim
+            qkv[:, :q_end] = (qkv[:, :q_end].float() * (1 + self.spec.q_rate * pos)).to(qkv.dtype)
+            qkv[:, q_end:k_end] = (qkv[:, q_end:k_end].float() / (1 + self.spec.k_rate * pos)).to(qkv.dtype)
+
+    register_part("toy_routed_ffn", ToyRoutedFFN, replace=True)
+    register_part("toy_scale_position", ToyScalePosition, replace=True)
+
+    def spec_of(raw: dict) -> ModelSpec:
+        h, eps = raw["hidden_size"], raw["eps"]
+        norm = NormSpec(h, eps)
+        scaled = AttentionSpec(h, 6, 3, 16, False, eps, False, 0.25, ToyScaleSpec(0.03, 0.05), None)
+        rotary = AttentionSpec(h, 6, 3, 16, True, eps, False, 0.25, RotarySpec(16, 1e4, 16), None)
+
+        def names(i):
+            return {"input_norm": f"l{i}.n1", "mixer": f"l{i}.mix", "post_norm": f"l{i}.n2", "ffn": f"l{i}.ffn"}
+
+        layers = (LayerSpec(norm, scaled, norm, ToyRoutedSpec(h, raw["inter"], raw["experts"]), names(0)),
+                  LayerSpec(norm, rotary, norm, GatedMLPSpec(h, raw["inter"]), names(1)))
+        schedule = (RunSpec(0), RunSpec(1))
+        return ModelSpec(raw["vocab"], h, layers, schedule, norm, True, 4096, (), "emb.weight", "fnorm", "head.weight")
+
+    register_architecture(Architecture("ToyRoutedForCausalLM", lambda raw: raw, spec_of), replace=True)
+
+
+def toy_routed_plain(ids, w, raw):
+    """Whole-sequence restatement with plain torch ops."""
+    h = w["emb.weight"][torch.tensor(ids)]
+    n, eps = len(ids), raw["eps"]
+    pos = torch.arange(n, dtype=torch.float32)
+
+    def norm(x, name):
+        return plain.rms_norm(x, w[name + ".weight"], eps)
+
+    def heads(x, p, which, count):
+        return (x @ w[f"{p}.{which}_proj.weight"].t()).view(n, count, 16)
+
+    def attend(q, k, v):
+        k, v = k.repeat_interleave(2, 1), v.repeat_interleave(2, 1)
+        s = torch.einsum("thd,shd->hts", q, k) * 0.25 + plain.causal_mask(n, q.dtype)
+        return torch.einsum("hts,shd->thd", torch.softmax(s, -1), v).reshape(n, 96)
+
+    # layer 0: scaled positions, routed feed-forward
+    x = norm(h, "l0.n1")
+    q, k, v = heads(x, "l0.mix", "q", 6), heads(x, "l0.mix", "k", 3), heads(x, "l0.mix", "v", 3)
+    q = q * (1 + 0.03 * pos)[:, None, None]
+    k = k / (1 + 0.05 * pos)[:, None, None]
+    h = h + attend(q, k, v) @ w["l0.mix.o_proj.weight"].t()
+    x = norm(h, "l0.n2")
+    prob = torch.softmax(x @ w["l0.ffn.router.weight"].t(), -1)
+    best = prob.argmax(-1)
+    update = torch.zeros_like(x)
+    for t in range(n):
+        e = int(best[t])
+        y = torch.relu(x[t] @ w[f"l0.ffn.experts.{e}.w1.weight"].t()) @ w[f"l0.ffn.experts.{e}.w2.weight"].t()
+        update[t] = prob[t, e] * y
+    h = h + update
+    # layer 1: per-head norms, rotation, gated feed-forward
+    x = norm(h, "l1.n1")
+    q, k, v = heads(x, "l1.mix", "q", 6), heads(x, "l1.mix", "k", 3), heads(x, "l1.mix", "v", 3)
+    q = plain.rms_norm(q, w["l1.mix.q_norm.weight"], eps)
+    k = plain.rms_norm(k, w["l1.mix.k_norm.weight"], eps)
+    cos, sin = plain.rotary_tables(torch.arange(n), 16, 1e4, torch.float32)
+    q, k = plain.apply_rotary(q.transpose(0, 1), cos, sin).transpose(0, 1), plain.apply_rotary(k.transpose(0, 1), cos, sin).transpose(0, 1)
+    h = h + attend(q, k, v) @ w["l1.mix.o_proj.weight"].t()
+    h = h + plain.feed_forward(norm(h, "l1.n2"), w, "l1.ffn")
+    return norm(h, "fnorm") @ w["emb.weight"].t()
+
+
+def test_toy_routed_feed_forward_and_position_encoding(fe, tmp_path) -> None:
+    """A feed-forward with routing and a position encoding of another kind, registered from
+    here, built layer by layer next to the package's own parts, and stepped whole and in
+    portions beside another request."""
+    from forge_engine_b200.config import read_model_config
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+    from forge_engine_b200.models import expected_tensors
+    from forge_engine_b200.weights import random_tensors, write_model_folder
+
+    register_toy_routed()
+    raw = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 80, "inter": 56, "experts": 3, "vocab": 101,
+           "eps": 1e-5}
+    _, _, spec = read_model_config(raw)
+    tensors = random_tensors(expected_tensors(spec), seed=3, std=0.15)
+    write_model_folder(tmp_path / "toy2", raw, tensors)
+    runner = ModelRunner.from_folder(tmp_path / "toy2", dtype="float32", page_size=4, num_pages=48, max_requests=2)
+    w = {k: v.float() for k, v in tensors.items()}
+    a, b = random_ids(101, 21, 5), random_ids(101, 12, 6)
+    ref_a, ref_b = toy_routed_plain(a, w, raw), toy_routed_plain(b, w, raw)
+    runner.begin("a")
+    whole = runner.step([StepEntry("a", a, range(21))]).cpu()
+    torch.testing.assert_close(whole, ref_a, atol=5e-5, rtol=1e-4)
+    runner.end("a")
+    runner.begin("a"), runner.begin("b")
+    rows_a, rows_b = [], []
+    cuts_a, cuts_b = [7, 2, 12], [1, 9, 2]
+    sa = sb = 0
+    for step in range(3):
+        out = runner.step([StepEntry("a", a[sa : sa + cuts_a[step]], range(cuts_a[step])),
+                           StepEntry("b", b[sb : sb + cuts_b[step]], range(cuts_b[step]))]).cpu()
+        rows_a.append(out[: cuts_a[step]])
+        rows_b.append(out[cuts_a[step] :])
+        sa += cuts_a[step]
+        sb += cuts_b[step]
+    runner.check_status()
+    torch.testing.assert_close(torch.cat(rows_a), ref_a, atol=5e-5, rtol=1e-4)
+    torch.testing.assert_close(torch.cat(rows_b), ref_b, atol=5e-5, rtol=1e-4)
+    runner.end("a"), runner.end("b")
+    runner.cache.check_consistency()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graph_replay_equals_eager_steps(fe, dtype, tmp_path) -> None:
     """Decode steps replayed from CUDA graphs (padded to bucket sizes, fixed table widths)
