@@ -170,6 +170,27 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
   }
 }
 
+// One finished value: feature `feature` (this lane's accumulator row) of token `token`.  All
+// lanes of the warp call it for the same token.
+template <int EPI>
+__device__ __forceinline__ void store_one(const GemmParams& p, float v, int feature, int token, int lane) {
+  if (EPI == EPI_SILU_MUL_BF16) {
+    // lanes 0-15 hold 16 gate features, lanes 16-31 the matching up features
+    const float up = __shfl_xor_sync(0xffffffffu, v, 16);
+    const int half_o = p.o >> 1;
+    const int out_feature = (feature >> 5) * 16 + (lane & 15);
+    if (lane < 16 && token < p.n && out_feature < half_o)
+      reinterpret_cast<bf16*>(p.y)[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(silu_f(v) * up);
+    return;
+  }
+  if (feature >= p.o || token >= p.n) return;
+  const size_t at = (size_t)token * p.o + feature;
+  const float r = v + (p.bias ? p.bias[feature] : 0.f);
+  if (EPI == EPI_STORE_BF16) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(r);
+  else if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(p.y)[at] = r;
+  else reinterpret_cast<float*>(p.y)[at] = __ldcg(reinterpret_cast<const float*>(p.y) + at) + r;
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
@@ -346,27 +367,32 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     unsigned rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-    if (rank == 0 && warp >= 2 && *abort_flag == 0) {
+    if (warp >= 2 && *abort_flag == 0) {
+      // every block of the cluster finishes a share of the tile's live tokens: it adds the
+      // blocks' partial values of those tokens in block order (the sum does not depend on
+      // timing, on the number of tokens or on which block does it) and stores them
       const int quarter = warp & 3;
-      const int feature = m0 + quarter * 32 + lane;
+      const int row = quarter * 32 + lane;
+      const int live = min(BN, p.n - n0);
+      const int share = (live + p.ksplit - 1) / p.ksplit;
+      const int t_begin = (int)rank * share, t_end = min(live, t_begin + share);
       const unsigned local = smem_u32(a_tiles);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float v[16];
+      unsigned remote[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-        for (int peer = 0; peer < p.ksplit; ++peer) {     // fixed order: the sum does not depend on timing
-          unsigned remote;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(peer));
+      for (int peer = 0; peer < 8; ++peer)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[peer]) : "r"(local), "r"(peer < p.ksplit ? peer : 0));
+      for (int t = t_begin; t < t_end; ++t) {
+        float part[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float part;
-            asm volatile("ld.shared::cluster.f32 %0, [%1];"
-                         : "=f"(part) : "r"(remote + (unsigned)(((c + j) * BM + quarter * 32 + lane) * 4)) : "memory");
-            v[j] += part;
-          }
+        for (int peer = 0; peer < 8; ++peer) {
+          part[peer] = 0.f;
+          if (peer < p.ksplit)
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[peer]) : "r"(remote[peer] + (unsigned)((t * BM + row) * 4)) : "memory");
         }
-        store16<EPI>(p, v, feature, n0 + c, lane);
+        float v = 0.f;
+#pragma unroll
+        for (int peer = 0; peer < 8; ++peer) v += part[peer];
+        store_one<EPI>(p, v, m0 + row, n0 + t, lane);
       }
     }
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // stashes stay alive until read
