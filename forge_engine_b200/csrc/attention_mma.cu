@@ -65,6 +65,7 @@ struct AttnParams {
   float* ws_acc;         // [entries, nkv, splits, 16, D]
   float* ws_ml;          // [entries, nkv, splits, 16, 2]
   unsigned* ws_count;    // [entries, nkv] zeroed arrival counters, or null: a merge kernel follows
+  int cluster_merge;     // the splits of a pair form a thread-block cluster and combine through shared memory
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) {
@@ -698,6 +699,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // merge the four consumer warps: reuse the key stages
   float* acc_s = reinterpret_cast<float*>(kbuf);          // [4][16][D]
   float* ml_s = acc_s + 4 * DEC_ROWS * D;                 // [4][16][2]
+  float* part_s = reinterpret_cast<float*>(vbuf);         // [16][D] this block's partial result (cluster merge)
+  float* part_ml_s = part_s + DEC_ROWS * D;               // [16][2]
   if (warp < 4) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -734,6 +737,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int token = row / p.groups, g = row - token * p.groups;
       p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
           __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else if (p.cluster_merge) {
+      part_s[row * D + d] = num;
+      if (d == 0) {
+        part_ml_s[row * 2] = big;
+        part_ml_s[row * 2 + 1] = den;
+      }
     } else {
       const size_t slot = pair * p.num_splits + split;
       p.ws_acc[(slot * DEC_ROWS + row) * D + d] = num;
@@ -745,6 +754,50 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
   if (tid == 0 && *abort_flag) atomicOr(p.status, FE_STATUS_WAIT_TIMEOUT);
   if (p.num_splits == 1) return;
+
+  if (p.cluster_merge) {
+    // The splits of this (entry, kv head) are the blocks of one cluster.  Every block
+    // finishes a share of the rows: it reads the blocks' partial results of those rows
+    // from their shared memory and combines them in block order.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const int splits = p.num_splits;
+    const int share = (rows_total + splits - 1) / splits;
+    const int row_begin = split * share, row_end = min(rows_total, row_begin + share);
+    const unsigned local_part = smem_addr(part_s), local_ml = smem_addr(part_ml_s);
+    for (int idx = tid; idx < (row_end - row_begin) * D; idx += TMA_THREADS) {
+      const int row = row_begin + idx / D, d = idx % D;
+      float mv[8], lv[8], av[8];
+#pragma unroll
+      for (int peer = 0; peer < 8; ++peer) {
+        mv[peer] = -INFINITY; lv[peer] = 0.f; av[peer] = 0.f;
+        if (peer < splits) {
+          unsigned remote_ml, remote_part;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_ml) : "r"(local_ml), "r"(peer));
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_part) : "r"(local_part), "r"(peer));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mv[peer]) : "r"(remote_ml + (unsigned)(row * 8)) : "memory");
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lv[peer]) : "r"(remote_ml + (unsigned)(row * 8 + 4)) : "memory");
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(av[peer]) : "r"(remote_part + (unsigned)((row * D + d) * 4)) : "memory");
+        }
+      }
+      float big = -INFINITY;
+#pragma unroll
+      for (int peer = 0; peer < 8; ++peer) big = fmaxf(big, mv[peer]);
+      float num = 0.f, den = 0.f;
+#pragma unroll
+      for (int peer = 0; peer < 8; ++peer) {
+        const float f = (mv[peer] == -INFINITY) ? 0.f : exp2f(mv[peer] - big);
+        num += av[peer] * f;
+        den += lv[peer] * f;
+      }
+      const int token = row / p.groups, g = row - token * p.groups;
+      p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
+          __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // partial results stay alive until read
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    return;
+  }
 
   // the block that publishes its partial result last combines all of them, in split order
   __threadfence();
@@ -946,6 +999,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
   p.ws_acc = workspace;
   p.ws_ml = workspace ? workspace + (size_t)entries * num_kv_heads * num_splits * DEC_ROWS * D : nullptr;
   p.ws_count = counters;
+  p.cluster_merge = 0;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1005,7 +1059,11 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
         if (e != cudaSuccess) return (int)e;
         tma_configured = true;
       }
-      rc = fe_launch_dependent(attn_decode_tma_kernel, grid, dim3(TMA_THREADS), DECODE_TMA_SMEM, stream, *mk, *mv, p);
+      // up to 8 splits: one cluster per (entry, kv head), partial results never leave the SMs
+      p.cluster_merge = (num_splits > 1 && num_splits <= 8) ? 1 : 0;
+      rc = fe_launch_dependent_shaped(attn_decode_tma_kernel, grid, dim3(TMA_THREADS), DECODE_TMA_SMEM, stream,
+                                      dim3(p.cluster_merge ? num_splits : 1, 1, 1), *mk, *mv, p);
+      p.cluster_merge = 0;
     } else {
       rc = fe_launch_dependent(attn_decode_kernel, grid, dim3(THREADS), DECODE_SMEM, stream, p);
     }
@@ -1079,6 +1137,7 @@ FE_EXPORT int SYM(fe_attention_decode_noalloc_d)(const void* q, int q_stride, vo
   p.ws_acc = scratch;
   p.ws_ml = scratch + (size_t)entries * num_kv_heads * num_splits * DEC_ROWS * D;
   p.ws_count = nullptr;
+  p.cluster_merge = 0;
   p.row_lo = 0; p.row_hi = DEC_ROWS;
   dim3 grid(num_splits, entries, num_kv_heads);
   attn_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(p);

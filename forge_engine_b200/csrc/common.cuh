@@ -138,11 +138,11 @@ static inline int fe_pdl_enabled() {
 
 // Launch `kernel` as a dependent of the kernel before it on `stream`.  Only for kernels that
 // call pdl_wait() before their first access to global memory another kernel may write.
-// cluster_z > 1 additionally groups that many consecutive blocks along z into one
-// thread-block cluster (they can then read one another's shared memory).
+// `cluster` with more than one block additionally groups that many consecutive blocks into
+// one thread-block cluster (they can then read one another's shared memory).
 template <typename... KArgs, typename... Args>
-static inline int fe_launch_dependent_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                              cudaStream_t stream, int cluster_z, Args&&... args) {
+static inline int fe_launch_dependent_shaped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                             cudaStream_t stream, dim3 cluster, Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -153,14 +153,22 @@ static inline int fe_launch_dependent_cluster(void (*kernel)(KArgs...), dim3 gri
   attribute[0].val.programmaticStreamSerializationAllowed = fe_pdl_enabled();
   config.attrs = attribute;
   config.numAttrs = 1;
-  if (cluster_z > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attribute[1].id = cudaLaunchAttributeClusterDimension;
-    attribute[1].val.clusterDim.x = 1;
-    attribute[1].val.clusterDim.y = 1;
-    attribute[1].val.clusterDim.z = (unsigned)cluster_z;
+    attribute[1].val.clusterDim.x = cluster.x;
+    attribute[1].val.clusterDim.y = cluster.y;
+    attribute[1].val.clusterDim.z = cluster.z;
     config.numAttrs = 2;
   }
   return (int)cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
+// Cluster of `cluster_z` blocks along the grid's z axis (1: no cluster).
+template <typename... KArgs, typename... Args>
+static inline int fe_launch_dependent_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                              cudaStream_t stream, int cluster_z, Args&&... args) {
+  return fe_launch_dependent_shaped(kernel, grid, block, smem, stream, dim3(1, 1, (unsigned)(cluster_z > 1 ? cluster_z : 1)),
+                                    std::forward<Args>(args)...);
 }
 
 template <typename... KArgs, typename... Args>
