@@ -146,10 +146,13 @@ __device__ __forceinline__ void load_kv_tile(bf16* kdst, bf16* vdst, const AttnP
 struct PaddedTile {
   static __device__ __forceinline__ const bf16* at(const bf16* base, int key, int col) { return base + key * LD + col; }
 };
-struct SwizzledTile {
+
+// A key's D elements lie together as D/64 lines of 128 bytes; the 128-byte swizzle goes by
+// the line (what one TMA box of a whole page chunk, seen as lines, leaves in shared memory).
+struct LineSwizzledTile {
   static __device__ __forceinline__ const bf16* at(const bf16* base, int key, int col) {
-    const int block = col >> 6, chunk = (col >> 3) & 7;
-    return base + block * (BN * 64) + key * 64 + ((chunk ^ (key & 7)) << 3);
+    const int line = key * (D / 64) + (col >> 6), chunk = (col >> 3) & 7;
+    return base + line * 64 + ((chunk ^ (line & 7)) << 3);
   }
 };
 
@@ -655,12 +658,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
               if (!dead) mbar_expect_tx(full + s, 2 * TILE_BYTES);
             }
             if (!dead) {
-#pragma unroll
-              for (int blk = 0; blk < D / 64; ++blk) {
-                const int offset = blk * (BN * 64) + pg * p.page_size * 64;
-                tma_load_2d(kbuf + s * (BN * D) + offset, &map_k, blk * 64, row, full + s);
-                tma_load_2d(vbuf + s * (BN * D) + offset, &map_v, blk * 64, row, full + s);
-              }
+              // one box per page and matrix: the page's keys of this head are contiguous
+              const int offset = pg * p.page_size * D;
+              tma_load_2d(kbuf + s * (BN * D) + offset, &map_k, 0, row * (D / 64), full + s);
+              tma_load_2d(vbuf + s * (BN * D) + offset, &map_v, 0, row * (D / 64), full + s);
             }
           }
         }
@@ -687,7 +688,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (!mbar_wait(full + s, (i / TMA_STAGES) & 1, abort_flag)) break;
         const int key0 = (tile_begin + i) * BN + warp * 16;
         if (key0 < key_end)
-          tile_step<16, SwizzledTile>(qf, kbuf + s * (BN * D), vbuf + s * (BN * D), warp * 16, key0, key_end, pos_a,
+          tile_step<16, LineSwizzledTile>(qf, kbuf + s * (BN * D), vbuf + s * (BN * D), warp * 16, key0, key_end, pos_a,
                                       pos_b, p.window, p.scale_log2, true, m, l, o, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);
@@ -944,17 +945,21 @@ bool ensure_encode() {
   return g_encode_tiled != nullptr;
 }
 
-const CUtensorMap* cache_map(const void* base, int rows, int page_size) {
-  static std::map<std::tuple<const void*, int, int>, CUtensorMap> maps;
-  const auto key = std::make_tuple(base, rows, page_size);
+const CUtensorMap* cache_map(const void* base, int rows, int page_size, bool lines = false) {
+  // lines: the matrix seen as [rows * D/64 lines, 64 columns]; a box is a whole page chunk
+  // (page_size * D/64 lines, contiguous in memory)
+  static std::map<std::tuple<const void*, int, int, bool>, CUtensorMap> maps;
+  const auto key = std::make_tuple(base, rows, page_size, lines);
   auto found = maps.find(key);
   if (found != maps.end()) return &found->second;
   if (!ensure_encode()) return nullptr;
   EncodeTiledFn encode = g_encode_tiled;
   CUtensorMap map;
-  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
+  const int per_row = lines ? D / 64 : 1;
+  if (page_size * per_row > 256) return nullptr;
+  cuuint64_t dims[2] = {(cuuint64_t)(lines ? 64 : D), (cuuint64_t)rows * per_row};
+  cuuint64_t strides[1] = {(cuuint64_t)(lines ? 64 : D) * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)(page_size * per_row)};
   cuuint32_t elem[2] = {1, 1};
   if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -1049,8 +1054,8 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
     dim3 grid(num_splits, entries, num_kv_heads);
     int rc = 0;
     const bool tma_ok = (D % 64) == 0 && page_size <= BN && (BN % page_size) == 0 && (num_splits == 1 || counters != nullptr);
-    const CUtensorMap* mk = tma_ok ? cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
-    const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
+    const CUtensorMap* mk = tma_ok ? cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size, true) : nullptr;
+    const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size, true) : nullptr;
     if (mk && mv) {
       static bool tma_configured = false;
       if (!tma_configured) {
