@@ -65,6 +65,18 @@ def test_prefill_and_decode_mixed(native, nq, nkv, d, page, window) -> None:
     run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits=3, sharp=True)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 8, 64, 8), (16, 8, 128, 32), (16, 2, 128, 64), (16, 1, 64, 128),
+                                           (8, 2, 128, 4), (6, 3, 128, 16)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_prefill_tensor_memory_kernel_shapes(native, nq, nkv, d, page, window) -> None:
+    """The tcgen05 prefill kernel at 1, 2, 4, 8 and 16 heads per kv head, page sizes from 4
+    to 128, prompts that end inside a query tile, inside a key tile and on their edges, a
+    portion that starts in the middle of a page, and a window that ends inside a tile."""
+    lengths = [700, 513, 384, 128, 257, 31]
+    new_counts = [700, 130, 384, 128, 64, 31]
+    run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits=2, sharp=True)
+
+
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
 def test_split_decode_long_contexts(native, splits) -> None:
     lengths = [2048, 1, 777, 64, 65, 4000]
