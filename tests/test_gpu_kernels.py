@@ -48,7 +48,7 @@ def test_embedding(native, dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("size", [72, 203, 2560, 5000])
+@pytest.mark.parametrize("size", [72, 203, 2560, 5000, 12292, 16384, 16388])
 def test_add_rmsnorm(native, dtype, size) -> None:
     g = torch.Generator().manual_seed(size)
     rows = 37
@@ -204,7 +204,8 @@ def test_attention_simt(native, dtype, nq, nkv, d, page, window) -> None:
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,d,rot,norm", [(8, 2, 32, 32, True), (6, 3, 48, 48, True), (32, 8, 128, 128, True),
-                                                (4, 1, 64, 32, True), (4, 2, 16, 16, False)])
+                                                (4, 1, 64, 32, True), (4, 2, 16, 16, False), (6, 2, 64, 64, True),
+                                                (3, 1, 256, 256, True), (5, 1, 128, 128, False)])
 def test_qk_rope_cache(native, dtype, nq, nkv, d, rot, norm) -> None:
     g = torch.Generator().manual_seed(d)
     page, theta, eps = 8, 12345.0, 2e-6
