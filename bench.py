@@ -48,6 +48,23 @@ CONFIG_4B = {
 }
 CONTEXT = 2048
 PAGE = 16
+
+# Two further shapes, run through the scheduler from prompts to the last token
+# (`--workload`): requests, prompt lengths (uniform range, ids from the given seed), new
+# tokens per request.
+WORKLOADS = {
+    "mixed-8b": {
+        "config": dict(CONFIG_4B, hidden_size=4096, intermediate_size=12288, rope_theta=1000000.0,
+                       max_position_embeddings=32768, tie_word_embeddings=False),
+        "requests": 64, "prompt_range": (16, 4096), "new_tokens": 256, "seed": 6, "token_budget": 2048,
+    },
+    "long-32b": {
+        "config": dict(CONFIG_4B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64,
+                       num_attention_heads=64, rope_theta=1000000.0, max_position_embeddings=16384,
+                       tie_word_embeddings=False),
+        "requests": 32, "prompt_range": (8192, 8192), "new_tokens": 128, "seed": 7, "token_budget": 2048,
+    },
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -200,6 +217,59 @@ def reference_arm(args) -> int:
         return 0
 
 
+def scheduler_workload(name: str, layers: int | None) -> int:
+    """All requests of the workload submitted at once; the scheduler cuts the prompts into
+    portions under its token budget beside the decoding requests.  Wall-clock time from
+    the first submit to the last token, host token ids in and out."""
+    import torch
+
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine
+    from forge_engine_b200.sampling import SamplingParams
+
+    work = WORKLOADS[name]
+    raw = dict(work["config"])
+    layers_full = raw["num_hidden_layers"]
+    if layers:
+        raw["num_hidden_layers"] = layers
+    gen = torch.Generator().manual_seed(work["seed"])
+    low, high = work["prompt_range"]
+    count, new = work["requests"], work["new_tokens"]
+    lengths = torch.randint(low, high + 1, (count,), generator=gen).tolist()
+    prompts = [torch.randint(0, raw["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
+    pages = sum(-(-(n + new) // PAGE) + 1 for n in lengths) + 64
+    engine = Engine.from_random(
+        raw, 0, engine_config=EngineConfig(max_new_tokens=new, dtype="bfloat16"),
+        scheduler_config=SchedulerConfig(max_requests=count, max_batch_size=count, token_budget=work["token_budget"],
+                                         block_size=PAGE, block_capacity=pages),
+        device="cuda:0")
+    engine.generate([prompts[0][:64]], SamplingParams(max_new_tokens=4))       # warm-up: builds, first launches
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    sampler.start()
+    begin = time.perf_counter()
+    outputs = engine.generate(prompts, SamplingParams(max_new_tokens=new, temperature=0.0))
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - begin
+    clocks = sampler.stop()
+    made = sum(len(o) for o in outputs)
+    print(json.dumps({
+        "metric": f"generated tok/s through the scheduler ({name})", "value": round(made / seconds, 1), "unit": "tokens/s",
+        "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "impl": "ours",
+        "data": f"synthetic token ids (seed {work['seed']}), random weights (seed 0)",
+        "seconds": round(seconds, 3), "generated": made, "prompt_tokens": sum(lengths),
+        "all_tokens_per_second": round((made + sum(lengths)) / seconds, 1),
+        "config": {"workload": name, "layers": raw["num_hidden_layers"], "layers_full": layers_full,
+                   "hidden": raw["hidden_size"], "q_heads": raw["num_attention_heads"],
+                   "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
+                   "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "requests": count,
+                   "prompt_min": low, "prompt_max": high, "new_tokens": new, "token_budget": work["token_budget"],
+                   "page_size": PAGE},
+        "clocks": clocks,
+    }))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -211,6 +281,8 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1/64, prefill and e2e")
     parser.add_argument("--prefill-only", action="store_true",
                         help="time only the 2,048-token prefill (small cases for profiling)")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS),
+                        help="instead of the decode benchmark: a whole workload through the scheduler")
     parser.add_argument("--kernel-times", action="store_true",
                         help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()
@@ -223,6 +295,8 @@ def main() -> int:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.workload:
+        return scheduler_workload(args.workload, args.layers)
 
     import torch
 
