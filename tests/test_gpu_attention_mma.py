@@ -77,6 +77,13 @@ def test_prefill_tensor_memory_kernel_shapes(native, nq, nkv, d, page, window) -
     run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits=2, sharp=True)
 
 
+def test_prefill_portion_deep_in_a_long_context(native) -> None:
+    """A 1,000-token portion that starts 5,000 tokens into its request (47 key tiles, the
+    rings of key and value stages wrap many times), beside a whole 3,000-token prompt."""
+    run_case(native, 8, 2, 128, 16, None, [6000, 3000], [1000, 3000], splits=1, sharp=True)
+    run_case(native, 8, 2, 128, 16, 1500, [6000, 3000], [1000, 3000], splits=1)
+
+
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
 def test_split_decode_long_contexts(native, splits) -> None:
     lengths = [2048, 1, 777, 64, 65, 4000]
