@@ -381,18 +381,28 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
       for (int peer = 0; peer < 8; ++peer)
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[peer]) : "r"(local), "r"(peer < p.ksplit ? peer : 0));
-      for (int t = t_begin; t < t_end; ++t) {
-        float part[8];
+      // four tokens at a time, so that their loads from the other blocks are in flight together
+      for (int t = t_begin; t < t_end; t += 4) {
+        float part[4][8];
 #pragma unroll
-        for (int peer = 0; peer < 8; ++peer) {
-          part[peer] = 0.f;
-          if (peer < p.ksplit)
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[peer]) : "r"(remote[peer] + (unsigned)((t * BM + row) * 4)) : "memory");
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int peer = 0; peer < 8; ++peer) {
+            part[u][peer] = 0.f;
+            if (peer < p.ksplit && t + u < t_end)
+              asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                           : "=f"(part[u][peer]) : "r"(remote[peer] + (unsigned)(((t + u) * BM + row) * 4)) : "memory");
+          }
         }
-        float v = 0.f;
 #pragma unroll
-        for (int peer = 0; peer < 8; ++peer) v += part[peer];
-        store_one<EPI>(p, v, m0 + row, n0 + t, lane);
+        for (int u = 0; u < 4; ++u) {
+          if (t + u < t_end) {        // the same for the whole block
+            float v = 0.f;
+#pragma unroll
+            for (int peer = 0; peer < 8; ++peer) v += part[u][peer];
+            store_one<EPI>(p, v, m0 + row, n0 + t + u, lane);
+          }
+        }
       }
     }
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // stashes stay alive until read
