@@ -191,12 +191,6 @@ __device__ __forceinline__ void tc5_st16(unsigned taddr, const unsigned (&r)[16]
       : "memory");
 }
 
-#ifdef FE_TC5_TRACE
-#define TC5_T(slot) do { if (trace) trace[(slot)] = clock64(); } while (0)
-#else
-#define TC5_T(slot) do { } while (0)
-#endif
-
 // The key range of one query tile, in key tiles of the block's own numbering.
 struct Tc5Tile {
   bool valid;
@@ -239,9 +233,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   pdl_trigger();
   const int entry = blockIdx.y, kvh = blockIdx.x;
-#ifdef FE_TC5_TRACE
-  long long* trace = (blockIdx.x == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) ? (long long*)p.ws_acc : nullptr;
-#endif
   const int tok0 = p.cu_tokens[entry];
   const int n_new = p.cu_tokens[entry + 1] - tok0;
   const int rows_total = n_new * p.groups;
@@ -377,10 +368,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int x = 0; x < 2 && ok; ++x) {
           if (active(x, i)) {
-            TC5_T(8192 + i * 16 + x * 8 + 0);
             ok = mbar_wait(p_full + x, done[x] & 1, abort_flag);
             if (!ok) break;
-            TC5_T(8192 + i * 16 + x * 8 + 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // O_x += P_x V : 8 steps of 16 keys; V is MN-major, 16 keys = 2048 bytes further down
             const uint64_t vb = v_desc + (uint64_t)(s * (TC5_KV_BYTES >> 4));
@@ -391,7 +380,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
               tc5_mma_ts_acc(o_dst, p_src + kk * 8, vb + (uint64_t)(kk * (2048 >> 4)), idesc_pv);
             tc5_commit(pv_done + x);
             ++done[x];
-            TC5_T(8192 + i * 16 + x * 8 + 2);
           }
           // the value stage may be refilled when the products issued so far are done
           if (x == 1) tc5_commit(v_empty + s);
@@ -404,7 +392,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
               keys_ready = true;
             }
             issue_scores(x, i + 1);
-            TC5_T(8192 + i * 16 + x * 8 + 3);
           }
         }
         if (!ok) break;
@@ -433,20 +420,14 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     unsigned count = 0;                                // key tiles this query tile has taken
     for (int i = 0; i < n_tiles && ok; ++i) {
       if (!active(x, i)) continue;
-#ifdef FE_TC5_TRACE
-      if (quarter != 0) trace = nullptr;
-#endif
-      TC5_T(x * 4096 + count * 8 + 0);
       ok = mbar_wait(s_full + x, count & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      TC5_T(x * 4096 + count * 8 + 1);
       const int key0 = (tile_begin + i) * TC5_KEYS;
       unsigned raw[TC5_KEYS];
 #pragma unroll
       for (int c = 0; c < TC5_KEYS / 32; ++c) tc5_ld32_issue(s_addr + c * 32, raw + c * 32);
       tc5_ld_wait();
-      TC5_T(x * 4096 + count * 8 + 2);
       // every key of the tile visible to every row of the tile?
       const bool clear = key0 + TC5_KEYS - 1 <= mine.pos_first && key0 + TC5_KEYS <= mine.key_end &&
                          mine.row0 + TC5_ROWS <= rows_total && (p.window <= 0 || mine.pos_last - key0 < p.window);
@@ -480,7 +461,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
       }
       const float neg_base = (m_used == -INFINITY) ? 0.f : -m_used;
-      TC5_T(x * 4096 + count * 8 + 3);
       // two scores at a time through the packed 32-bit multiply-add and add
       const uint64_t scale2 = tc5_pair(p.scale_log2, p.scale_log2), base2 = tc5_pair(neg_base, neg_base);
       uint64_t sum_a = tc5_pair(0.f, 0.f), sum_b = sum_a;
@@ -502,7 +482,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       float sum0, sum1;
       tc5_unpair(tc5_add2(sum_a, sum_b), sum0, sum1);
       l = l * corr + (sum0 + sum1);
-      TC5_T(x * 4096 + count * 8 + 4);
       // O_x is only touched once the previous value product of this tile has finished;
       // the next one is not issued before this warp has arrived below
       if (count > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
@@ -522,7 +501,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + x);
-      TC5_T(x * 4096 + count * 8 + 5);
       ++count;
     }
     // final: normalise and store this row
