@@ -79,12 +79,6 @@ __device__ __forceinline__ unsigned tc5_idesc(int m, int n, bool b_mn_major) {
   d |= (unsigned)(m >> 4) << 24;
   return d;
 }
-__device__ __forceinline__ void tc5_mma_ss(unsigned tmem_d, uint64_t da, uint64_t db, unsigned idesc, unsigned acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
-}
 __device__ __forceinline__ void tc5_mma_ts(unsigned tmem_d, unsigned tmem_a, uint64_t db, unsigned idesc, unsigned acc) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
