@@ -21,6 +21,8 @@ from .linear import Linear, fuse_rows
 # Two blocks of the split decode kernel fit on an SM (148 SMs on a B200).
 DECODE_SLOTS = 296
 MAX_SPLITS = 64   # what the merge takes
+CLUSTER_SPLITS = 8            # up to this many blocks combine their results inside a cluster
+CLUSTER_WORTH_TILES = 200     # ... which saves about as much as 100 more tiles per block cost
 
 
 def choose_splits(pairs: int, tiles: int) -> int:
@@ -29,11 +31,16 @@ def choose_splits(pairs: int, tiles: int) -> int:
     Few pairs: fill the machine's slots once, every block getting at least four 64-key
     tiles.  With more pairs than half the slots the machine is full anyway and splitting
     only adds partial results to combine (measured: one split is fastest at 512 pairs of
-    2,048 keys; very long contexts take two)."""
+    2,048 keys; very long contexts take two).  Up to 8 blocks combine their partial results
+    through shared memory; more go through global memory and a last-arriver merge that
+    costs about 10 us (measured at 16 splits), which only long contexts repay."""
     most = max(1, min(MAX_SPLITS, tiles // 4))
     if pairs * 2 > DECODE_SLOTS:
         return 1 if tiles <= 64 else min(most, 2)
-    return max(1, min(most, DECODE_SLOTS // pairs))
+    splits = max(1, min(most, DECODE_SLOTS // pairs))
+    if splits > CLUSTER_SPLITS and tiles < CLUSTER_WORTH_TILES:
+        splits = CLUSTER_SPLITS
+    return splits
 
 
 class GQAttention(Mixer):
