@@ -706,12 +706,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int row = half ? rb : ra;
-      float* dst = acc_s + ((size_t)warp * DEC_ROWS + row) * D + 2 * (lane & 3);
+      if (row >= rows_total) continue;          // rows without a query are not read below
+      float2* dst = reinterpret_cast<float2*>(acc_s + ((size_t)warp * DEC_ROWS + row) * D + 2 * (lane & 3));
 #pragma unroll
-      for (int n = 0; n < D / 8; ++n) {
-        dst[n * 8] = o[n][2 * half];
-        dst[n * 8 + 1] = o[n][2 * half + 1];
-      }
+      for (int n = 0; n < D / 8; ++n) dst[n * 4] = make_float2(o[n][2 * half], o[n][2 * half + 1]);
       if ((lane & 3) == 0) {
         ml_s[(warp * DEC_ROWS + row) * 2] = m[half];
         ml_s[(warp * DEC_ROWS + row) * 2 + 1] = l[half];
