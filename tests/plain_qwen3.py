@@ -360,6 +360,26 @@ TINY_D = dict(
 )
 
 
+# Head size 64 (the tensor-memory prefill kernel and the TMA decode kernel take it), two
+# heads per kv head, the second layer windowed with a window that ends inside a key tile.
+TINY_E = dict(
+    TINY_A,
+    vocab_size=311,
+    hidden_size=96,
+    intermediate_size=144,
+    num_hidden_layers=2,
+    num_attention_heads=4,
+    num_key_value_heads=2,
+    head_dim=64,
+    rms_norm_eps=1e-5,
+    rope_theta=100000.0,
+    use_sliding_window=True,
+    sliding_window=70,
+    max_window_layers=1,
+    eos_token_id=310,
+)
+
+
 def tensor_shapes(cfg: PlainConfig) -> dict[str, tuple[int, ...]]:
     """Tensor names and shapes of a checkpoint (src/forge_engine/weights.py:253-282)."""
     h, i = cfg.hidden_size, cfg.intermediate_size

@@ -30,9 +30,11 @@ CONFIGS = {
     "B": (plain.TINY_B, 2, 16),
     "C": (plain.TINY_C, 5, 8),
     "D": (plain.TINY_D, 6, 4),
+    "E": (plain.TINY_E, 7, 16),
 }
 LENGTHS = {"A": (70, 41, 97, 33, 52, 64), "B": (1 + 32, 7 + 32, 75, 40, 129, 48),
-           "C": (66, 35, 50, 81, 34, 47), "D": (90, 37, 58, 44, 71, 33)}
+           "C": (66, 35, 50, 81, 34, 47), "D": (90, 37, 58, 44, 71, 33),
+           "E": (200, 150, 170, 140, 260, 130)}
 
 
 def total_variation(a: np.ndarray, b: np.ndarray) -> float:
