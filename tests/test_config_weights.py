@@ -23,7 +23,7 @@ from forge_engine_b200.weights import load_checkpoint, random_tensors, write_mod
 
 
 def test_reads_every_size_from_config_json() -> None:
-    for raw in (plain.TINY_A, plain.TINY_B, plain.TINY_C, plain.TINY_D):
+    for raw in (plain.TINY_A, plain.TINY_B, plain.TINY_C, plain.TINY_D, plain.TINY_E):
         arch, cfg, spec = read_model_config(raw)
         assert arch.name == "Qwen3ForCausalLM"
         assert cfg.vocab_size == raw["vocab_size"] and cfg.head_dim == raw["head_dim"]
