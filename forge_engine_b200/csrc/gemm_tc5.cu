@@ -33,7 +33,25 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr unsigned WAIT_LIMIT = 20000000u;
 
-enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3 };
+enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3, EPI_QKV_ROPE = 4 };
+
+// What the fused q/k/v projection needs beyond the product (EPI_QKV_ROPE; head size 128, so
+// that a 128-feature tile is one head): per-head RMS norm of q and k with one [128] weight
+// each (src/forge_engine/qwen3.py:141-150), the half-split rotation (qwen3.py:345-381) and
+// the write of k and v into their cache pages (src/forge_engine/cache.py:385-416).  q is
+// stored rotated into y; k and v go to the pages only.
+struct QkvRope {
+  const float* q_weight;   // [128] or null: no norm
+  const float* k_weight;
+  float eps;
+  const float2* table;     // [n, 64] (cos, sin) of every token's angles, or null: no rotation
+  const int* positions;    // [n] position of every token in its request
+  const int* token_entry;  // [n] row of the block table
+  bf16* k_cache;           // [pages, kv heads, page_size, 128]
+  bf16* v_cache;
+  const int* block_table;  // [entries, max_pages]
+  int max_pages, page_size, num_pages, num_q_heads, num_kv_heads, write_kv;
+};
 
 struct GemmParams {
   void* y;
@@ -45,6 +63,7 @@ struct GemmParams {
   float* ws_part;        // [feature tiles, token tiles, ksplit, BN, BM] floats
   unsigned* ws_count;    // [feature tiles * token tiles], zero before and after a launch
   int* status;
+  QkvRope rope;          // EPI_QKV_ROPE only
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -170,6 +189,59 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
   }
 }
 
+// EPI_QKV_ROPE: the 128 epilogue threads hold one head's 128 values of one token.  `turn`
+// alternates between two sets of exchange buffers so that one named barrier per step is
+// enough.  Same arithmetic as qk_rope_cache.cu, on the 32-bit sums instead of their
+// bfloat16 roundings.
+__device__ __forceinline__ void rope_token(const GemmParams& p, float v, int head, int d, int token, float* exchange,
+                                           int turn, int quarter, int lane) {
+  const QkvRope& r = p.rope;
+  const bool live = token < p.n;
+  const bool is_q = head < r.num_q_heads, is_k = !is_q && head < r.num_q_heads + r.num_kv_heads;
+  float* sums = exchange + turn * 136;      // [4] warps' sums of squares, then [128] normalised values
+  float* values = sums + 8;
+  float out = v + (p.bias ? p.bias[head * 128 + d] : 0.f);
+  const int pos = live ? r.positions[token] : 0;
+  if (is_q || is_k) {
+    const float* w = is_q ? r.q_weight : r.k_weight;
+    if (w) {
+      float ss = out * out;
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, offset);
+      if (lane == 0) sums[quarter] = ss;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ss = ((sums[0] + sums[1]) + sums[2]) + sums[3];
+      out = out * rsqrtf(ss / 128.f + r.eps) * w[d];
+    }
+    if (r.table) {
+      values[d] = out;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const float partner = values[d ^ 64];
+      const float2 cs = live ? r.table[(size_t)token * 64 + (d & 63)] : make_float2(1.f, 0.f);
+      out = d < 64 ? out * cs.x - partner * cs.y : out * cs.x + partner * cs.y;
+    }
+  }
+  if (!live) return;
+  if (is_q) {
+    reinterpret_cast<bf16*>(p.y)[(size_t)token * p.o + head * 128 + d] = __float2bfloat16_rn(out);
+    return;
+  }
+  if (!r.write_kv) return;
+  const int logical = pos / r.page_size, slot = pos - logical * r.page_size;
+  if (pos < 0 || logical >= r.max_pages) {
+    if (d == 0 && p.status) atomicOr(p.status, FE_STATUS_BAD_POSITION);
+    return;
+  }
+  const int page = r.block_table[(size_t)r.token_entry[token] * r.max_pages + logical];
+  if (page < 0 || page >= r.num_pages) {
+    if (d == 0 && p.status) atomicOr(p.status, FE_STATUS_BAD_PAGE);
+    return;
+  }
+  const int kvh = is_k ? head - r.num_q_heads : head - r.num_q_heads - r.num_kv_heads;
+  bf16* cache = is_k ? r.k_cache : r.v_cache;
+  cache[(((size_t)page * r.num_kv_heads + kvh) * r.page_size + slot) * 128 + d] = __float2bfloat16_rn(out);
+}
+
 // One finished value: feature `feature` (this lane's accumulator row) of token `token`.  All
 // lanes of the warp call it for the same token.
 template <int EPI>
@@ -208,6 +280,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
+  float* exchange = reinterpret_cast<float*>(last_flag + 2);     // EPI_QKV_ROPE: 2 x 136 floats
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
@@ -300,7 +373,12 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
         }
-        store16<EPI>(p, v, feature, n0 + c, lane);
+        if (EPI == EPI_QKV_ROPE) {
+#pragma unroll 1
+          for (int j = 0; j < 16; ++j) rope_token(p, v[j], blockIdx.x, quarter * 32 + lane, n0 + c + j, exchange, j & 1, quarter, lane);
+        } else {
+          store16<EPI>(p, v, feature, n0 + c, lane);
+        }
       }
     } else if (ok && p.cluster_reduce) {
       // stash the partial tile in this block's shared memory ([token][feature], over the
@@ -355,7 +433,12 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             for (int j = 0; j < 16; ++j)
               v[j] += __ldcg(all + (size_t)sp * (BN * BM) + (size_t)(c + j) * BM + quarter * 32 + lane);
           }
-          store16<EPI>(p, v, feature, n0 + c, lane);
+          if (EPI == EPI_QKV_ROPE) {
+#pragma unroll 1
+            for (int j = 0; j < 16; ++j) rope_token(p, v[j], blockIdx.x, quarter * 32 + lane, n0 + c + j, exchange, j & 1, quarter, lane);
+          } else {
+            store16<EPI>(p, v, feature, n0 + c, lane);
+          }
         }
       }
     }
@@ -400,7 +483,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             float v = 0.f;
 #pragma unroll
             for (int peer = 0; peer < 8; ++peer) v += part[u][peer];
-            store_one<EPI>(p, v, m0 + row, n0 + t + u, lane);
+            if (EPI == EPI_QKV_ROPE) rope_token(p, v, blockIdx.x, row, n0 + t + u, exchange, (t + u) & 1, quarter, lane);
+            else store_one<EPI>(p, v, m0 + row, n0 + t + u, lane);
           }
         }
       }
@@ -418,7 +502,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 }
 
 template <int BN> constexpr size_t smem_bytes() {
-  return (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + (2 * stages_for<BN>() + 1) * 8 + 16 + 1024;
+  return (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + (2 * stages_for<BN>() + 1) * 8 + 16 + 2 * 136 * 4 + 1024;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -474,6 +558,9 @@ int launch_bn(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
     case EPI_STORE_F32: return launch_one<BN, EPI_STORE_F32>(mw, mx, p, grid, stream);
     case EPI_ADD_F32: return launch_one<BN, EPI_ADD_F32>(mw, mx, p, grid, stream);
     case EPI_SILU_MUL_BF16: return launch_one<BN, EPI_SILU_MUL_BF16>(mw, mx, p, grid, stream);
+    case EPI_QKV_ROPE:
+      if (BN <= 64) return launch_one<(BN <= 64 ? BN : 16), EPI_QKV_ROPE>(mw, mx, p, grid, stream);
+      return FE_ERR_BAD_SHAPE;
   }
   return FE_ERR_BAD_DTYPE;
 }
@@ -483,13 +570,8 @@ int launch_bn(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
 // Token-tile width the kernel uses for n tokens.
 FE_EXPORT int fe_gemm_tc5_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256))); }
 
-// epilogue: 0 store bf16 [n, o]; 1 store f32 [n, o]; 2 add into f32 [n, o];
-// 3 y[n, o/2] = silu(gate) * up (bf16) for w whose rows alternate 16 gate, 16 up features.
-// ksplit > 1 needs ws_part (floats: feature tiles * token tiles * ksplit * tile * 128) and
-// ws_count (one zeroed unsigned per output tile; left zeroed).
-FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
-                          int epilogue, int ksplit, float* ws_part, unsigned* ws_count, int* status,
-                          cudaStream_t stream) {
+static int run_gemm(const void* x, const void* w, const float* bias, void* y, int n, int o, int k, int epilogue, int ksplit,
+                    float* ws_part, unsigned* ws_count, int* status, const QkvRope* rope, cudaStream_t stream) {
   if (n <= 0 || o <= 0) return 0;
   if (k <= 0 || (k % 8) != 0) return FE_ERR_BAD_SHAPE;
   if (epilogue == EPI_SILU_MUL_BF16 && ((o % 32) != 0 || bias != nullptr)) return FE_ERR_BAD_SHAPE;
@@ -505,7 +587,7 @@ FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void*
   rc = make_map(&mx, x, n, k, bn);
   if (rc) return rc;
   const int cluster_reduce = (ksplit > 1 && ksplit <= 8 && bn <= 64) ? 1 : 0;
-  GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, ws_part, ws_count, status};
+  GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, ws_part, ws_count, status, rope ? *rope : QkvRope{}};
   dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
   if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;
   switch (bn) {
@@ -515,4 +597,34 @@ FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void*
     case 128: return launch_bn<128>(mw, mx, p, grid, stream);
     default: return launch_bn<256>(mw, mx, p, grid, stream);
   }
+}
+
+// epilogue: 0 store bf16 [n, o]; 1 store f32 [n, o]; 2 add into f32 [n, o];
+// 3 y[n, o/2] = silu(gate) * up (bf16) for w whose rows alternate 16 gate, 16 up features.
+// ksplit > 1 needs ws_part (floats: feature tiles * token tiles * ksplit * tile * 128) and
+// ws_count (one zeroed unsigned per output tile; left zeroed).
+FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
+                          int epilogue, int ksplit, float* ws_part, unsigned* ws_count, int* status,
+                          cudaStream_t stream) {
+  if (epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) return FE_ERR_BAD_DTYPE;
+  return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream);
+}
+
+// The fused q/k/v projection of up to 64 tokens with 128-wide heads: y [n, (nq + 2 nkv) * 128]
+// receives the normalised, rotated queries; keys (normalised, rotated) and values go straight
+// into their cache pages [pages, nkv, page_size, 128].  q_weight / k_weight may be null (no
+// norm); table is the (cos, sin) table of fe_rope_table for these tokens, or null (no rotation).
+FE_EXPORT int fe_gemm_tc5_qkv_rope(const void* x, const void* w, const float* bias, void* y, int n, int k, int ksplit,
+                                   const float* q_weight, const float* k_weight, float eps, const void* table,
+                                   const int* positions, const int* token_entry, void* k_cache, void* v_cache,
+                                   const int* block_table, int max_pages, int page_size, int num_pages,
+                                   int num_q_heads, int num_kv_heads, int write_kv, int* status,
+                                   cudaStream_t stream) {
+  if (n > 64 || num_q_heads < 1 || num_kv_heads < 1 || page_size < 1) return FE_ERR_BAD_SHAPE;
+  static_assert(BM == 128, "a feature tile is one head of 128");
+  const int o = (num_q_heads + 2 * num_kv_heads) * 128;
+  const int ks = ksplit < 1 ? 1 : (ksplit > 8 ? 8 : ksplit);     // splits beyond a cluster would need the workspace
+  QkvRope rope{q_weight, k_weight, eps, (const float2*)table, positions, token_entry, (bf16*)k_cache, (bf16*)v_cache,
+               block_table, max_pages, page_size, num_pages, num_q_heads, num_kv_heads, write_kv};
+  return run_gemm(x, w, bias, y, n, o, k, EPI_QKV_ROPE, ks, nullptr, nullptr, status, &rope, stream);
 }

@@ -14,8 +14,8 @@
 template <typename T>
 __global__ void qk_rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight,
                                      const float* __restrict__ k_weight, float eps,
-                                     const float* __restrict__ inv_freq, int rotary_dim,
-                                     const int* __restrict__ positions,
+                                     const float* __restrict__ inv_freq, const float2* __restrict__ table,
+                                     int rotary_dim, const int* __restrict__ positions,
                                      const int* __restrict__ token_entry, PagedKV cache,
                                      int num_q_heads, int write_kv, int* status) {
   pdl_trigger();
@@ -77,7 +77,11 @@ __global__ void qk_rope_cache_kernel(T* __restrict__ qkv, const float* __restric
       float a = to_float(x[j]) * inv, b = to_float(x[j + half]) * inv;
       if (w) { a *= w[j]; b *= w[j + half]; }
       float c = 1.f, s = 0.f;
-      if (inv_freq) {
+      if (table) {
+        const float2 cs = table[(size_t)token * half + j];
+        c = cs.x;
+        s = cs.y;
+      } else if (inv_freq) {
         const float angle = (float)pos * inv_freq[j];
         c = cosf(angle);
         s = sinf(angle);
@@ -104,7 +108,8 @@ __global__ void qk_rope_cache_kernel(T* __restrict__ qkv, const float* __restric
 template <int D>
 __global__ void qk_rope_cache_vec_kernel(bf16* __restrict__ qkv, const float* __restrict__ q_weight,
                                          const float* __restrict__ k_weight, float eps,
-                                         const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                         const float* __restrict__ inv_freq, const float2* __restrict__ table,
+                                         const int* __restrict__ positions,
                                          const int* __restrict__ token_entry, PagedKV cache, int num_q_heads,
                                          int write_kv, int* status) {
   constexpr int LANES = D / 8;            // lanes per head
@@ -142,7 +147,11 @@ __global__ void qk_rope_cache_vec_kernel(bf16* __restrict__ qkv, const float* __
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     cs[e] = 1.f; sn[e] = 0.f;
-    if (inv_freq) {
+    if (table) {
+      const float2 both = table[(size_t)token * HALF + j0 + e];
+      cs[e] = both.x;
+      sn[e] = both.y;
+    } else if (inv_freq) {
       const float angle = (float)pos * inv_freq[j0 + e];
       cs[e] = cosf(angle);
       sn[e] = sinf(angle);
@@ -188,8 +197,30 @@ __global__ void qk_rope_cache_vec_kernel(bf16* __restrict__ qkv, const float* __
   }
 }
 
+// cos and sin of float(position) * inv_freq[j] for every token and pair j, taken once per
+// step: table [n, half] of (cos, sin).  The angles are the same in every layer.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half, int n,
+                                  float2* __restrict__ table) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * half) return;
+  const int token = i / half, j = i - token * half;
+  const float angle = (float)positions[token] * inv_freq[j];
+  table[i] = make_float2(cosf(angle), sinf(angle));
+}
+
+FE_EXPORT int fe_rope_table(const int* positions, const float* inv_freq, int half, int n, void* table, cudaStream_t stream) {
+  if (n <= 0 || half <= 0) return 0;
+  const int threads = 128;
+  return fe_launch_dependent(rope_table_kernel, dim3((n * half + threads - 1) / threads), dim3(threads), 0, stream, positions,
+                             inv_freq, half, n, (float2*)table);
+}
+
+// `table` (optional): the output of fe_rope_table for these tokens and inv_freq; without it
+// the kernel takes cosine and sine itself.
 FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, const float* k_weight,
-                               float eps, const float* inv_freq, int rotary_dim,
+                               float eps, const float* inv_freq, const void* table, int rotary_dim,
                                const int* positions, const int* token_entry, void* k_cache,
                                void* v_cache, const int* block_table, int max_pages,
                                int page_size, int num_pages, int num_q_heads, int num_kv_heads,
@@ -219,7 +250,8 @@ FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, cons
     dim3 vgrid(n_tokens, (need + w - 1) / w);
 #define LAUNCH_VEC(DIM)                                                                                         \
     return fe_launch_dependent(qk_rope_cache_vec_kernel<DIM>, vgrid, dim3(w * 32), 0, stream, (bf16*)qkv, q_weight, \
-                               k_weight, eps, inv_freq, positions, token_entry, cache, num_q_heads, write_kv, status)
+                               k_weight, eps, inv_freq, (const float2*)table, positions, token_entry, cache, num_q_heads,  \
+                               write_kv, status)
     if (head_dim == 64) LAUNCH_VEC(64);
     if (head_dim == 128) LAUNCH_VEC(128);
     LAUNCH_VEC(256);
@@ -227,10 +259,10 @@ FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, cons
   }
   if (dtype == FE_DTYPE_F32)
     return fe_launch_dependent(qk_rope_cache_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)qkv, q_weight, k_weight,
-        eps, inv_freq, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
+        eps, inv_freq, (const float2*)table, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
   else if (dtype == FE_DTYPE_BF16)
     return fe_launch_dependent(qk_rope_cache_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (bf16*)qkv, q_weight, k_weight,
-        eps, inv_freq, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
+        eps, inv_freq, (const float2*)table, rotary_dim, positions, token_entry, cache, num_q_heads, write_kv, status);
   else
     return FE_ERR_BAD_DTYPE;
   return fe_last_error();

@@ -34,6 +34,7 @@ class StepBatch:
     want_rows: [W] - flat token indices whose logits are returned;
     group_tables[g]: [R, P_g] - block table of every entry in layer group g (-1: no page).
     ``entries`` repeats (slot, start, count) on the host for parts written in Python.
+    ``shared`` holds what parts work out once per step for all layers (keyed by them).
     """
 
     n_tokens: int
@@ -51,6 +52,7 @@ class StepBatch:
     entries: list = field(default_factory=list)
     max_new: int = 0
     max_ctx: int = 0
+    shared: dict = field(default_factory=dict)
 
 
 @dataclass

@@ -101,6 +101,7 @@ class DecoderModel:
     def forward(self, batch, cache) -> torch.Tensor:
         """Run ``batch`` through all runs; returns logits [wanted rows, vocab] in 32-bit."""
         n = batch.n_tokens
+        batch.shared.clear()      # what parts share lives for one pass only (a batch may be run again)
         h = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.ctx.device)
         native.embedding(batch.token_ids, self.embed, h, self.ctx.status)
         pending = None

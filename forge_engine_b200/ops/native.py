@@ -58,11 +58,13 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_embedding": [p, p, i, p, i, i, i, p, p],
         "fe_add_rmsnorm": [p, p, i, p, p, i, p, i, i, f, i, p],
         "fe_silu_mul": [p, p, i, i, i, i, p],
-        "fe_qk_rope_cache": [p, i, p, p, f, p, i, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
+        "fe_qk_rope_cache": [p, i, p, p, f, p, p, i, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
+        "fe_rope_table": [p, p, i, i, p, p],
         "fe_attention_simt": [p, i, i, p, p, p, i, i, i, p, p, i, f, p, i, i, i, i, p, p],
         "fe_gemm_simt": [p, i, p, i, p, p, i, i, i, i, i, p],
         "fe_sample": [p, i, i, p, p, p, p, p, p, p, p, p],
         "fe_gemm_tc5": [p, p, p, p, i, i, i, i, i, p, p, p, p],
+        "fe_gemm_tc5_qkv_rope": [p, p, p, p, i, i, i, p, p, f, p, p, p, p, p, p, i, i, i, i, i, i, p, p],
     }
     for name, argtypes in signatures.items():
         fn = getattr(handle, name)
@@ -193,6 +195,15 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     check(lib().fe_silu_mul(ptr(gate_up), ptr(out), code(out), rows, inter, int(block), stream()), "silu_mul")
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
+    """table[t, j] = (cos, sin) of float(positions[t]) * inv_freq[j], in 32-bit."""
+    _dense(positions, "positions"), _dense(inv_freq, "inv_freq"), _dense(table, "table")
+    n, half = positions.numel(), inv_freq.numel()
+    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float32
+    assert table.dtype == torch.float32 and table.shape == (n, half, 2)
+    check(lib().fe_rope_table(ptr(positions), ptr(inv_freq), half, n, ptr(table), stream()), "rope_table")
+
+
 def qk_rope_cache(
     qkv: torch.Tensor,
     q_weight: torch.Tensor | None,
@@ -208,10 +219,12 @@ def qk_rope_cache(
     num_q_heads: int,
     write_kv: bool,
     status: torch.Tensor,
+    table: torch.Tensor | None = None,
 ) -> None:
     """Normalise and rotate q (in place) and k, and store k, v into their pages.
 
-    qkv is [N, (nq + 2 nkv) * D]; the caches are [pages, nkv, page_size, D]."""
+    qkv is [N, (nq + 2 nkv) * D]; the caches are [pages, nkv, page_size, D].  ``table``:
+    ``rope_table`` of these tokens (then the kernel does not take cosine and sine itself)."""
     _dense(qkv, "qkv"), _dense(k_cache, "k_cache"), _dense(v_cache, "v_cache")
     _dense(block_table, "block_table")
     num_pages, nkv, page_size, head_dim = k_cache.shape
@@ -220,11 +233,12 @@ def qk_rope_cache(
     assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
     assert block_table.dtype == torch.int32 and block_table.dim() == 2
     assert positions.dtype == torch.int32 and token_entry.dtype == torch.int32
-    for w in (q_weight, k_weight, inv_freq):
+    for w in (q_weight, k_weight, inv_freq, table):
         assert w is None or (w.dtype == torch.float32 and w.is_cuda and w.is_contiguous())
+    assert table is None or (inv_freq is not None and table.shape == (n, rotary_dim // 2, 2))
     check(
         lib().fe_qk_rope_cache(
-            ptr(qkv), code(qkv), ptr(q_weight), ptr(k_weight), float(eps), ptr(inv_freq),
+            ptr(qkv), code(qkv), ptr(q_weight), ptr(k_weight), float(eps), ptr(inv_freq), ptr(table),
             int(rotary_dim), ptr(positions), ptr(token_entry), ptr(k_cache), ptr(v_cache),
             ptr(block_table), block_table.shape[1], page_size, num_pages, num_q_heads, nkv,
             head_dim, n, 1 if write_kv else 0, ptr(status), stream(),
@@ -398,6 +412,54 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
     check(lib().fe_gemm_tc5(ptr(x), ptr(w), ptr(bias), ptr(out), n, o, k, int(epilogue), ksplit, ptr(part),
                             ptr(count), ptr(status), stream()),
           "gemm_tc5")
+
+
+def gemm_tc5_qkv_rope(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: torch.Tensor | None,
+    qkv: torch.Tensor,
+    q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None,
+    eps: float,
+    table: torch.Tensor | None,
+    positions: torch.Tensor,
+    token_entry: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    num_q_heads: int,
+    write_kv: bool,
+    status: torch.Tensor,
+    ksplit: int = 1,
+) -> None:
+    """The fused q/k/v projection of up to 64 tokens for heads of 128: x @ w.T on tcgen05,
+    then per head the q/k RMS norm, the rotation and - for keys and values - the write into
+    the cache pages, all in the product's epilogue.  ``qkv`` [n, (nq + 2 nkv) * 128] receives
+    the finished queries (its key and value columns are not written).  ``table`` is the
+    ``rope_table`` of these tokens [n, 64, 2], or None for no rotation."""
+    _dense(x, "x"), _dense(w, "w"), _dense(qkv, "qkv"), _dense(k_cache, "k_cache"), _dense(v_cache, "v_cache")
+    _dense(block_table, "block_table")
+    n, k = x.shape
+    num_pages, nkv, page_size, head_dim = k_cache.shape
+    assert head_dim == 128 and n <= TC5_MAX_ROWS
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
+    assert k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16
+    assert w.shape == ((num_q_heads + 2 * nkv) * 128, k) and qkv.shape == (n, w.shape[0])
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2
+    assert positions.dtype == torch.int32 and token_entry.dtype == torch.int32
+    for name, t in (("q_weight", q_weight), ("k_weight", k_weight), ("table", table), ("bias", bias)):
+        assert t is None or (t.dtype == torch.float32 and t.is_cuda and t.is_contiguous()), \
+            f"{name}: a contiguous 32-bit tensor on the GPU is needed, got {t.dtype} on {t.device}"
+    assert table is None or table.shape == (n, 64, 2)
+    check(
+        lib().fe_gemm_tc5_qkv_rope(
+            ptr(x), ptr(w), ptr(bias), ptr(qkv), n, k, max(1, min(8, int(ksplit))), ptr(q_weight), ptr(k_weight),
+            float(eps), ptr(table), ptr(positions), ptr(token_entry), ptr(k_cache), ptr(v_cache), ptr(block_table),
+            block_table.shape[1], page_size, num_pages, num_q_heads, nkv, 1 if write_kv else 0, ptr(status), stream(),
+        ),
+        "gemm_tc5_qkv_rope",
+    )
 
 
 def sample(

@@ -9,6 +9,8 @@ head_dim, window) between steps.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..cache.manager import CacheNeeds, PagedKVSpec
@@ -21,6 +23,9 @@ from .linear import Linear, fuse_rows
 # Two blocks of the split decode kernel fit on an SM (148 SMs on a B200).
 DECODE_SLOTS = 296
 MAX_SPLITS = 64   # what the merge takes
+# With more tokens a block of the projection finishes so many that the separate kernel is
+# faster (measured: 2.35 -> 2.27 ms per step at 1 token, no change at 8, 6.2 -> 6.7 ms at 64).
+FUSED_PROJECTION_ROWS = 16
 CLUSTER_SPLITS = 8            # up to this many blocks combine their results inside a cluster
 CLUSTER_WORTH_TILES = 200     # ... which saves about as much as 100 more tiles per block cost
 
@@ -95,20 +100,34 @@ class GQAttention(Mixer):
         return CacheNeeds(kv=PagedKVSpec(self.nkv, self.d, self.spec.window))
 
     def forward(self, x, batch, cache: CacheView):
-        qkv = self.qkv_proj(x)
         k_cache, v_cache = cache.kv
         table = batch.group_tables[cache.group]
         rotary = self.position.rotary()
-        if rotary is None:
-            self.position.apply(qkv, self.nq, self.nkv, self.d, batch)
-            inv_freq, rotary_dim = None, 0
+        if self._fused_projection(x, rotary, k_cache):
+            # few tokens, heads of 128: norm, rotation and the page write happen in the
+            # projection's own epilogue
+            qkv = torch.empty((x.shape[0], self.qkv_proj.out_features), dtype=x.dtype, device=x.device)
+            native.gemm_tc5_qkv_rope(
+                x, self.qkv_proj.weight, self.qkv_proj.bias, qkv, self.q_norm, self.k_norm,
+                self.spec.qk_norm_eps, self.position.table(batch), batch.positions, batch.token_entry, k_cache, v_cache, table,
+                self.nq, cache.owns, self.ctx.status,
+                ksplit=native.tc5_ksplit(self.qkv_proj.out_features, self.qkv_proj.in_features),
+            )
         else:
-            inv_freq, rotary_dim = rotary
-        native.qk_rope_cache(
-            qkv, self.q_norm, self.k_norm, self.spec.qk_norm_eps, inv_freq, rotary_dim,
-            batch.positions, batch.token_entry, k_cache, v_cache, table, self.nq,
-            cache.owns, self.ctx.status,
-        )
+            qkv = self.qkv_proj(x)
+            angles = None
+            if rotary is None:
+                self.position.apply(qkv, self.nq, self.nkv, self.d, batch)
+                inv_freq, rotary_dim = None, 0
+            else:
+                inv_freq, rotary_dim = rotary
+                if hasattr(self.position, "table"):
+                    angles = self.position.table(batch)
+            native.qk_rope_cache(
+                qkv, self.q_norm, self.k_norm, self.spec.qk_norm_eps, inv_freq, rotary_dim,
+                batch.positions, batch.token_entry, k_cache, v_cache, table, self.nq,
+                cache.owns, self.ctx.status, table=angles,
+            )
         out = torch.empty((x.shape[0], self.nq * self.d), dtype=qkv.dtype, device=x.device)
         groups = self.nq // self.nkv
         if qkv.dtype == torch.bfloat16 and groups <= native.ATTN_DECODE_ROWS:
@@ -119,6 +138,14 @@ class GQAttention(Mixer):
                 self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
             )
         return self.o_proj(out)
+
+    def _fused_projection(self, x, rotary, k_cache) -> bool:
+        """Whether the q/k/v projection's epilogue can do the per-head norms, the rotation
+        and the page write: the tcgen05 kernel takes the call, a head is one 128-feature
+        tile, and the whole head is rotated."""
+        return (self.d == 128 and rotary is not None and rotary[1] == 128 and k_cache.dtype == torch.bfloat16
+                and x.shape[0] <= FUSED_PROJECTION_ROWS and self.qkv_proj._tc5_ok(x)
+                and os.environ.get("FORGE_ENGINE_FUSED_QKV", "1") != "0")
 
     def _tensor_core_attention(self, qkv, k_cache, v_cache, table, batch, out, groups) -> None:
         """Entries with few rows (new tokens x heads per kv head <= 16) take the split

@@ -250,6 +250,18 @@ def test_qk_rope_cache(native, dtype, nq, nkv, d, rot, norm) -> None:
         page_id = int(table[e, p // page])
         torch.testing.assert_close(k_cache[page_id, :, p % page].float().cpu(), k_ref[i], **bound)
         assert torch.equal(v_cache[page_id, :, p % page].cpu(), v[i].to(dtype))
+    # with the angles' cosines and sines taken beforehand: the same bits
+    angles = torch.empty((n, rot // 2, 2), dtype=torch.float32, device=DEV)
+    native.rope_table(torch.tensor(positions, dtype=torch.int32, device=DEV), inv_freq.to(DEV), angles)
+    reference = torch.stack((torch.cos(pos[:, None].double() * inv_freq.double()), torch.sin(pos[:, None].double() * inv_freq.double())), -1)
+    torch.testing.assert_close(angles.double().cpu(), reference, atol=2e-6, rtol=0)
+    again, k2, v2 = qkv.clone().to(DEV), torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    native.qk_rope_cache(
+        again, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, eps, inv_freq.to(DEV), rot,
+        torch.tensor(positions, dtype=torch.int32, device=DEV), torch.tensor(entry, dtype=torch.int32, device=DEV),
+        k2, v2, table, nq, True, status, table=angles,
+    )
+    assert torch.equal(again, dev_qkv) and torch.equal(k2, k_cache) and torch.equal(v2, v_cache)
     # slots that no token of this step owns stay untouched (zero)
     assert float(k_cache[2].abs().sum()) == 0 and float(k_cache[3].abs().sum()) == 0
     assert float(k_cache[4, :, :5].abs().sum()) == 0    # positions 8..12 of request 0 live in page 1 (pages 4,1,6)
@@ -425,6 +437,74 @@ def test_gemm_tc5(native, n, o, k, ksplit) -> None:
     # a second launch finds the arrival counters zeroed again
     native.gemm_tc5(x, w, out, native.TC5_STORE_F32, status, ksplit=ksplit)
     torch.testing.assert_close(out.double(), ref, atol=2e-4, rtol=1e-5)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("n,nq,nkv,k,ksplit,norm,rotate", [(1, 2, 1, 128, 1, True, True), (17, 4, 2, 200, 2, True, True),
+                                                          (8, 32, 8, 2560, 4, True, True), (64, 3, 3, 512, 8, False, True),
+                                                          (33, 4, 1, 256, 3, True, False)])
+def test_gemm_tc5_qkv_rope(native, n, nq, nkv, k, ksplit, norm, rotate) -> None:
+    """The q/k/v projection with the per-head norms, the rotation and the page write in its
+    epilogue, against the same steps in 64-bit from the same bfloat16 inputs."""
+    d, page, theta, eps = 128, 8, 54321.0, 3e-6
+    g = torch.Generator().manual_seed(n + k)
+    x = torch.randn((n, k), generator=g).bfloat16()
+    w = (torch.randn(((nq + 2 * nkv) * d, k), generator=g) * (k ** -0.5)).bfloat16()
+    bias = torch.randn((nq + 2 * nkv) * d, generator=g) * 0.1
+    qw, kw = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    # two requests: the first already holds 37 tokens; pages in scrambled order
+    first = (n + 1) // 2
+    positions = list(range(37, 37 + first)) + list(range(0, n - first))
+    entry = [0] * first + [1] * (n - first)
+    pages_each = -(-(37 + n) // page)
+    order = torch.randperm(2 * pages_each, generator=g).to(torch.int32)
+    table = order.view(2, pages_each).to(DEV)
+    k_cache = torch.zeros((2 * pages_each, nkv, page, d), dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    qkv = torch.full((n, (nq + 2 * nkv) * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = status_word()
+    cos_sin = None
+    if rotate:
+        cos_sin = torch.empty((n, d // 2, 2), dtype=torch.float32, device=DEV)
+        native.rope_table(torch.tensor(positions, dtype=torch.int32, device=DEV), inv_freq.to(DEV), cos_sin)
+    native.gemm_tc5_qkv_rope(
+        x.to(DEV), w.to(DEV), bias.to(DEV), qkv, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, eps,
+        cos_sin, torch.tensor(positions, dtype=torch.int32, device=DEV),
+        torch.tensor(entry, dtype=torch.int32, device=DEV), k_cache, v_cache, table, nq, True, status, ksplit=ksplit)
+    assert int(status.item()) == 0
+    y = x.double() @ w.double().t() + bias.double()
+    q = y[:, : nq * d].view(n, nq, d)
+    kk = y[:, nq * d : (nq + nkv) * d].view(n, nkv, d)
+    v = y[:, (nq + nkv) * d :].view(n, nkv, d)
+    if norm:
+        q = q * torch.rsqrt(q.square().mean(-1, keepdim=True) + eps) * qw.double()
+        kk = kk * torch.rsqrt(kk.square().mean(-1, keepdim=True) + eps) * kw.double()
+    if rotate:
+        angles = torch.tensor(positions, dtype=torch.float64)[:, None] * inv_freq.double()[None, :]
+        cosine, sine = torch.cat((angles, angles), -1).cos()[:, None, :], torch.cat((angles, angles), -1).sin()[:, None, :]
+        turn = lambda t: t * cosine + torch.cat((-t[..., d // 2 :], t[..., : d // 2]), -1) * sine
+        q, kk = turn(q), turn(kk)
+    bound = dict(atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(qkv[:, : nq * d].double().cpu().view(n, nq, d), q, **bound)
+    for i, (e, p) in enumerate(zip(entry, positions)):
+        page_id = int(table[e, p // page])
+        torch.testing.assert_close(k_cache[page_id, :, p % page].double().cpu(), kk[i], **bound)
+        torch.testing.assert_close(v_cache[page_id, :, p % page].double().cpu(), v[i], **bound)
+    # nothing else was written: as many slots are non-zero as tokens were stored
+    assert int((k_cache.abs().sum((1, 3)) > 0).sum()) == n
+    # a row's result does not depend on the rows beside it
+    if n > 1:
+        alone = torch.empty((1, (nq + 2 * nkv) * d), dtype=torch.bfloat16, device=DEV)
+        k2, v2 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+        native.gemm_tc5_qkv_rope(
+            x[:1].contiguous().to(DEV), w.to(DEV), bias.to(DEV), alone, qw.to(DEV) if norm else None,
+            kw.to(DEV) if norm else None, eps, cos_sin[:1].contiguous() if rotate else None,
+            torch.tensor(positions[:1], dtype=torch.int32, device=DEV), torch.tensor(entry[:1], dtype=torch.int32, device=DEV),
+            k2, v2, table, nq, True, status, ksplit=ksplit)
+        assert torch.equal(alone[:, : nq * d], qkv[:1, : nq * d])
+        page_id = int(table[0, positions[0] // page])
+        assert torch.equal(k2[page_id, :, positions[0] % page], k_cache[page_id, :, positions[0] % page])
     assert int(status.item()) == 0
 
 
