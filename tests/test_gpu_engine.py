@@ -757,6 +757,64 @@ def test_lookahead_gives_the_same_tokens_as_synchronous_steps(fe, tmp_path) -> N
     assert greedy_tokens == plain.greedy_generate(prompts[0], len(greedy_tokens), weights, plain.PlainConfig.from_dict(raw))
 
 
+def test_arrivals_cancellations_and_few_pages_under_lookahead(fe, tmp_path) -> None:
+    """Thirty greedy requests of random lengths arrive while others decode, some are
+    cancelled half-way, and the pool is so small that admission has to wait for pages:
+    every finished request equals the plain implementation's greedy continuation, and
+    every page and slot is back at the end."""
+    import random
+
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine
+    from forge_engine_b200.sampling import SamplingParams
+
+    cfg, weights = make_model_folder(tmp_path / "m", plain.TINY_A, 0)
+    rng = random.Random(11)
+    jobs = []
+    for i in range(30):
+        prompt = random_ids(cfg.vocab_size, rng.randint(1, 60), 500 + i)
+        jobs.append((prompt, rng.randint(1, 24), rng.random() < 0.2))       # prompt, new tokens, cancel it?
+    engine = Engine.from_pretrained(
+        tmp_path / "m", engine_config=EngineConfig(dtype="float32"),
+        scheduler_config=SchedulerConfig(max_requests=40, block_size=4, block_capacity=70, token_budget=48, max_batch_size=6,
+                                         chunk_size=16, lookahead=True))
+    submitted, cancelled = {}, set()
+    waiting = list(enumerate(jobs))
+    steps = 0
+    while waiting or not engine.scheduler.idle:
+        # two or three arrivals every few steps
+        if waiting and steps % 3 == 0:
+            for _ in range(min(len(waiting), rng.randint(1, 3))):
+                index, (prompt, new, _) = waiting.pop(0)
+                submitted[index] = engine.submit(prompt, sampling_params=SamplingParams(max_new_tokens=new))
+        engine.step()
+        steps += 1
+        for index, rid in submitted.items():
+            if jobs[index][2] and index not in cancelled:
+                view = engine.scheduler.request(rid)
+                if len(view.output_tokens) >= max(1, jobs[index][1] // 2) and not view.finish_reason:
+                    engine.cancel(rid)
+                    cancelled.add(index)
+        assert steps < 3000
+    engine.runner.check_status()
+    finished = 0
+    for index, rid in submitted.items():
+        view = engine.scheduler.request(rid)
+        prompt, new, _ = jobs[index]
+        want = plain.greedy_generate(prompt, new, weights, cfg)
+        got = list(view.output_tokens)
+        if index in cancelled:
+            assert got == want[: len(got)]
+        else:
+            # generation stops early only on an end-of-sequence id, which is not emitted
+            assert got == want[: len(got)] and (len(got) == new or view.finish_reason == "stop")
+            finished += 1
+    assert finished >= 15 and len(cancelled) >= 3 and finished + len(cancelled) == 30
+    snap = engine.scheduler.snapshot()
+    assert snap.allocated_blocks == (0,) and snap.reserved_blocks == (0,) and snap.running == 0
+    engine.runner.cache.check_consistency()
+
+
 def test_benchmark_layer_shapes_in_32_bit_and_bfloat16(fe, tmp_path) -> None:
     """Two layers with the layer sizes of the 4B benchmark model (hidden 2560, 32/8 heads of
     128, intermediate 9728, theta 5e6) and a vocabulary that is no multiple of 128: the
