@@ -150,9 +150,10 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 
 template <int BN> __host__ __device__ constexpr int stages_for() {
   // stage = weight tile (16 KB) + token tile (BN * 128 B).  Narrow token tiles keep the ring
-  // at about 100 KB, two blocks per SM, so that one block's epilogue and set-up overlap
-  // another's streaming; the widest tile takes the SM alone.
-  return BN <= 32 ? 6 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4));
+  // at about 100 KB (108, 100 and 96 KB for 16, 32 and 64 tokens), two blocks per SM, so that
+  // one block's epilogue and set-up overlap another's streaming and a product's 150-190
+  // blocks all run at once; the widest tile takes the SM alone.
+  return BN <= 16 ? 6 : (BN <= 32 ? 5 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4)));
 }
 
 // Finished values of one accumulator row (feature) for 16 consecutive tokens.
