@@ -113,7 +113,14 @@ def require_cuda() -> None:
         raise CUDAUnavailableError("no CUDA device: this engine runs on the GPU only")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream() -> int:
+    """Handle of the current CUDA stream of the current device (asked for at every launch: a
+    graph capture runs on a stream of its own)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
