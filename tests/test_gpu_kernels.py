@@ -48,10 +48,10 @@ def test_embedding(native, dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [37, 300])
 @pytest.mark.parametrize("size", [72, 203, 2560, 5000, 12292, 16384, 16388])
-def test_add_rmsnorm(native, dtype, size) -> None:
+def test_add_rmsnorm(native, dtype, size, rows) -> None:
     g = torch.Generator().manual_seed(size)
-    rows = 37
     residual = torch.randn((rows, size), generator=g).to(DEV)
     update = torch.randn((rows, size), generator=g).to(dtype).to(DEV)
     weight = (1 + 0.1 * torch.randn(size, generator=g)).to(DEV)
