@@ -273,7 +273,8 @@ def scheduler_workload(name: str, layers: int | None) -> int:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=None,
+                        help="timed steps (default 200; 20 for --impl reference, whose step takes a third of a second)")
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has")
@@ -286,6 +287,8 @@ def main() -> int:
     parser.add_argument("--kernel-times", action="store_true",
                         help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()
+    if args.steps is None:
+        args.steps = 20 if args.impl == "reference" else 200
     if args.impl == "reference":
         if args.gpus != 1:
             print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
