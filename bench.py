@@ -270,6 +270,67 @@ def scheduler_workload(name: str, layers: int | None) -> int:
     return 0
 
 
+def kernel_shapes() -> int:
+    """The three kernel shapes upstream publishes (docs/benchmarks.md:27-29, measured there on
+    an L4 with 10 warm-up and 50 timed iterations, CUDA events, median): this repository's
+    kernels at the same shapes, same method."""
+    import torch
+
+    from forge_engine_b200.ops import native
+
+    native.lib()
+    device = "cuda:0"
+    gen = torch.Generator().manual_seed(5)
+
+    def median_ms(run) -> float:
+        for _ in range(10):
+            run()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(50):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            run()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(begin.elapsed_time(end))
+        return statistics.median(times)
+
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    results = {}
+    # fused residual add + RMSNorm, [512, 2560] bfloat16
+    residual = torch.randn((512, 2560), generator=gen).to(device)
+    update = torch.randn((512, 2560), generator=gen).bfloat16().to(device)
+    weight = torch.ones(2560, device=device)
+    out = torch.empty((512, 2560), dtype=torch.bfloat16, device=device)
+    results["add_rmsnorm_512x2560_ms"] = round(median_ms(lambda: native.add_rmsnorm(residual, update, weight, out, 1e-6)), 4)
+    # paged single-token decode attention: 127 cached keys, 32 q heads, 8 kv heads, head size 128, one request
+    nq, nkv, d, page = 32, 8, 128, 16
+    k_cache = torch.randn((16, nkv, page, d), generator=gen).bfloat16().to(device)
+    v_cache = torch.randn((16, nkv, page, d), generator=gen).bfloat16().to(device)
+    table = torch.arange(8, dtype=torch.int32, device=device).view(1, 8)
+    q = torch.randn((1, (nq + 2 * nkv) * d), generator=gen).bfloat16().to(device)
+    o = torch.empty((1, nq * d), dtype=torch.bfloat16, device=device)
+    cu = torch.tensor([0, 1], dtype=torch.int32, device=device)
+    starts = torch.tensor([127], dtype=torch.int32, device=device)
+    results["paged_decode_past127_ms"] = round(median_ms(lambda: native.attention_mma(
+        q, q.shape[1], k_cache, v_cache, table, cu, starts, 1, 1, None, d ** -0.5, o, nq, status, False, True, 1)), 4)
+    # causal prefill attention, 128 tokens, 8 heads of 128 (8 kv heads)
+    q2 = torch.randn((128, 3 * 8 * d), generator=gen).bfloat16().to(device)
+    o2 = torch.empty((128, 8 * d), dtype=torch.bfloat16, device=device)
+    k2 = torch.randn((16, 8, page, d), generator=gen).bfloat16().to(device)
+    v2 = torch.randn((16, 8, page, d), generator=gen).bfloat16().to(device)
+    cu2 = torch.tensor([0, 128], dtype=torch.int32, device=device)
+    starts2 = torch.tensor([0], dtype=torch.int32, device=device)
+    results["causal_prefill_8x128x128_ms"] = round(median_ms(lambda: native.attention_mma(
+        q2, q2.shape[1], k2, v2, table, cu2, starts2, 1, 128, None, d ** -0.5, o2, 8, status, True, False, 1)), 4)
+    assert int(status.item()) == 0
+    print(json.dumps({"metric": "kernel time at the shapes upstream publishes", "unit": "ms", "impl": "ours", **results,
+                      "upstream_on_L4": {"add_rmsnorm_512x2560_ms": 0.0850, "paged_decode_past127_ms": 0.1004,
+                                         "causal_prefill_8x128x128_ms": 0.0891}}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -284,6 +345,8 @@ def main() -> int:
                         help="time only the 2,048-token prefill (small cases for profiling)")
     parser.add_argument("--workload", choices=sorted(WORKLOADS),
                         help="instead of the decode benchmark: a whole workload through the scheduler")
+    parser.add_argument("--kernels", action="store_true",
+                        help="instead: this repository's kernels at the three kernel shapes upstream publishes")
     parser.add_argument("--kernel-times", action="store_true",
                         help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()
@@ -300,6 +363,8 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.workload:
         return scheduler_workload(args.workload, args.layers)
+    if args.kernels:
+        return kernel_shapes()
 
     import torch
 
