@@ -65,7 +65,8 @@ struct AttnParams {
   float* ws_acc;         // [entries, nkv, splits, 16, D]
   float* ws_ml;          // [entries, nkv, splits, 16, 2]
   unsigned* ws_count;    // [entries, nkv] zeroed arrival counters, or null: a merge kernel follows
-  int cluster_merge;     // the splits of a pair form a thread-block cluster and combine through shared memory
+  int cluster_merge;     // 1: the splits of a pair form one cluster and combine through shared memory;
+                         // 2: clusters of 8 splits do, and the clusters' results go through the workspace
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) {
@@ -760,9 +761,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // from their shared memory and combines them in block order.
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    const int splits = p.num_splits;
+    // cluster_merge 2: clusters of 8; what a cluster combines is one partial result of several
+    const int splits = p.cluster_merge == 2 ? 8 : p.num_splits;
+    const int rank = split % splits;
     const int share = (rows_total + splits - 1) / splits;
-    const int row_begin = split * share, row_end = min(rows_total, row_begin + share);
+    const int row_begin = rank * share, row_end = min(rows_total, row_begin + share);
     const unsigned local_part = smem_addr(part_s), local_ml = smem_addr(part_ml_s);
     for (int idx = tid; idx < (row_end - row_begin) * D; idx += TMA_THREADS) {
       const int row = row_begin + idx / D, d = idx % D;
@@ -789,16 +792,26 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         num += av[peer] * f;
         den += lv[peer] * f;
       }
-      const int token = row / p.groups, g = row - token * p.groups;
-      p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
-          __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      if (p.cluster_merge == 2) {
+        const size_t slot = pair * (p.num_splits / 8) + split / 8;
+        p.ws_acc[(slot * DEC_ROWS + row) * D + d] = num;
+        if (d == 0) {
+          p.ws_ml[(slot * DEC_ROWS + row) * 2] = big;
+          p.ws_ml[(slot * DEC_ROWS + row) * 2 + 1] = den;
+        }
+      } else {
+        const int token = row / p.groups, g = row - token * p.groups;
+        p.out[((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D + d] =
+            __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      }
     }
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // partial results stay alive until read
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    return;
+    if (p.cluster_merge != 2) return;
   }
 
-  // the block that publishes its partial result last combines all of them, in split order
+  // the block that publishes its (or its cluster's) partial result last combines all of
+  // them, in split order
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -810,7 +823,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (!last_block) return;
   __threadfence();
   float* weight_s = reinterpret_cast<float*>(kbuf);       // [16][MERGE_MAX_SPLITS]
-  const int splits = p.num_splits;
+  const int splits = p.cluster_merge == 2 ? p.num_splits / 8 : p.num_splits;
   const size_t slot0 = pair * splits;
   for (int row = warp; row < rows_total; row += TMA_THREADS / 32) {
     float mv[MERGE_MAX_SPLITS / 32], lv[MERGE_MAX_SPLITS / 32];
@@ -1062,10 +1075,11 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
         if (e != cudaSuccess) return (int)e;
         tma_configured = true;
       }
-      // up to 8 splits: one cluster per (entry, kv head), partial results never leave the SMs
-      p.cluster_merge = (num_splits > 1 && num_splits <= 8) ? 1 : 0;
+      // up to 8 splits: one cluster per (entry, kv head), partial results never leave the SMs;
+      // a multiple of 8: clusters of 8 combine theirs first, the last block to arrive the clusters'
+      p.cluster_merge = (num_splits > 1 && num_splits <= 8) ? 1 : ((num_splits > 8 && num_splits % 8 == 0) ? 2 : 0);
       rc = fe_launch_dependent_shaped(attn_decode_tma_kernel, grid, dim3(TMA_THREADS), DECODE_TMA_SMEM, stream,
-                                      dim3(p.cluster_merge ? num_splits : 1, 1, 1), *mk, *mv, p);
+                                      dim3(p.cluster_merge == 1 ? num_splits : (p.cluster_merge == 2 ? 8 : 1), 1, 1), *mk, *mv, p);
       p.cluster_merge = 0;
     } else {
       rc = fe_launch_dependent(attn_decode_kernel, grid, dim3(THREADS), DECODE_SMEM, stream, p);
