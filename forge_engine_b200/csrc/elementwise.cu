@@ -238,8 +238,8 @@ __global__ void silu_mul_vec8_kernel(const T* __restrict__ gate_up, T* __restric
   int ga, ua;
   silu_sources(i, inter, block, &ga, &ua);   // block is a multiple of 8, so 8 features stay together
   float a[8], b[8];
-  load8(g + ga, a);
-  load8(g + ua, b);
+  load8_streaming(g + ga, a);      // gate and up are read once: they need not stay in the caches
+  load8_streaming(g + ua, b);
 #pragma unroll
   for (int k = 0; k < 8; ++k) a[k] = silu(a[k]) * b[k];
   store8(o + i, a);
