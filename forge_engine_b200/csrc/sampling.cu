@@ -4,7 +4,10 @@
 // the k-th largest value and the nucleus boundary are found by a 4-pass radix
 // search over an order-preserving integer image of the shifted logits, with counts
 // and fixed-point probability mass per digit, so that the result does not depend on
-// the order in which threads arrive.
+// the order in which threads arrive.  Groups of warps count into histograms of their own
+// in shared memory (a vocabulary's keys fall into a handful of digits in the first pass: one
+// shared histogram would serialise 150,000 atomic adds on five addresses), and the
+// histograms are added up after each pass.
 //
 // Ties: among values equal to the k-th largest, the lowest indices are kept (exactly
 // k survive).  Values equal to the nucleus boundary are all kept.
@@ -16,6 +19,7 @@
 #define FE_STATUS_BAD_LOGITS 16
 #define SMP_THREADS 1024
 #define MASS_SCALE 1099511627776.0f  // 2^40
+#define SMP_GROUPS 8                 // histogram copies; warp w counts into copy w % 8
 
 __host__ __device__ inline unsigned long long splitmix64(unsigned long long z) {
   z += 0x9E3779B97F4A7C15ull;
@@ -84,6 +88,9 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   __shared__ int red_i[32];
   __shared__ unsigned int hist_n[256];
   __shared__ unsigned long long hist_m[256];
+  __shared__ unsigned long long group_m[SMP_GROUPS * 256];
+  __shared__ unsigned int group_n[SMP_GROUPS * 256];
+  const int group = (threadIdx.x >> 5) % SMP_GROUPS;
   __shared__ unsigned long long scan_u[33];
   __shared__ float scan_f[33];
   __shared__ int scan_i[33];
@@ -142,13 +149,30 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   if (k > 0 && k < vocab) {
     if (tid == 0) { sh_prefix = 0u; sh_remaining = k; }
     for (int shift = 24; shift >= 0; shift -= 8) {
-      if (tid < 256) hist_n[tid] = 0u;
+      for (int b = tid; b < SMP_GROUPS * 256; b += SMP_THREADS) group_n[b] = 0u;
       __syncthreads();
       const unsigned int prefix = sh_prefix;
       const unsigned int mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-      for (int i = tid; i < vocab; i += SMP_THREADS) {
-        const unsigned int key = float_key(SHIFTED(i));
-        if ((key & mask) == prefix) atomicAdd(&hist_n[(key >> shift) & 255u], 1u);
+      if (shift == 24) {
+        // first pass: every key takes part and they fall into a handful of digits; lanes of
+        // a warp that hit the same digit add together, one atomic per digit and warp step
+        for (int base = 0; base < vocab; base += SMP_THREADS) {
+          const int i = base + tid;
+          const unsigned int digit = i < vocab ? (float_key(SHIFTED(i)) >> 24) : 0xffffffffu;
+          const unsigned int peers = __match_any_sync(0xffffffffu, digit);
+          if (digit != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&group_n[group * 256 + digit], (unsigned int)__popc(peers));
+        }
+      } else {
+        for (int i = tid; i < vocab; i += SMP_THREADS) {
+          const unsigned int key = float_key(SHIFTED(i));
+          if ((key & mask) == prefix) atomicAdd(&group_n[group * 256 + ((key >> shift) & 255u)], 1u);
+        }
+      }
+      __syncthreads();
+      if (tid < 256) {
+        unsigned int total_n = 0u;
+        for (int w = 0; w < SMP_GROUPS; ++w) total_n += group_n[w * 256 + tid];
+        hist_n[tid] = total_n;
       }
       __syncthreads();
       if (tid == 0) {
@@ -191,27 +215,60 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (tid == 0) { sh_prefix = 0u; sh_mass_above = 0ull; }
     unsigned long long limit = 0ull;
     for (int shift = 24; shift >= 0; shift -= 8) {
-      if (tid < 256) { hist_n[tid] = 0u; hist_m[tid] = 0ull; }
+      for (int b = tid; b < SMP_GROUPS * 256; b += SMP_THREADS) { group_n[b] = 0u; group_m[b] = 0ull; }
       __syncthreads();
       const unsigned int prefix = sh_prefix;
       const unsigned int mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
       unsigned long long local_total = 0ull;
-      for (int i = tid; i < vocab; i += SMP_THREADS) {
-        const float s = SHIFTED(i);
-        const unsigned int key = float_key(s);
-        const float w = expf(s);
-        if (!survives(keep, key, i, w)) continue;
-        const unsigned long long mass = (unsigned long long)(w * MASS_SCALE);
-        if (shift == 24) local_total += mass;
-        if ((key & mask) == prefix) {
-          atomicAdd(&hist_n[(key >> shift) & 255u], 1u);
-          atomicAdd(&hist_m[(key >> shift) & 255u], mass);
+      if (shift == 24) {
+        // first pass: the survivors fall into a handful of digits.  Lanes that hit the same
+        // digit add their masses together (in two 20-bit halves, so that 32 of them fit the
+        // 32-bit warp reduction) and one of them does the atomics
+        for (int base = 0; base < vocab; base += SMP_THREADS) {
+          const int i = base + tid;
+          unsigned int digit = 0xffffffffu;
+          unsigned long long mass = 0ull;
+          if (i < vocab) {
+            const float s = SHIFTED(i);
+            const unsigned int key = float_key(s);
+            const float w = expf(s);
+            if (survives(keep, key, i, w)) {
+              mass = (unsigned long long)(w * MASS_SCALE);      // at most 2^40
+              local_total += mass;
+              digit = key >> 24;
+            }
+          }
+          const unsigned int peers = __match_any_sync(0xffffffffu, digit);
+          const unsigned int low = __reduce_add_sync(peers, (unsigned int)(mass & 0xfffffull));
+          const unsigned int high = __reduce_add_sync(peers, (unsigned int)(mass >> 20));
+          if (digit != 0xffffffffu && lane == __ffs(peers) - 1) {
+            atomicAdd(&group_n[group * 256 + digit], (unsigned int)__popc(peers));
+            atomicAdd(&group_m[group * 256 + digit], ((unsigned long long)high << 20) + low);
+          }
+        }
+      } else {
+        for (int i = tid; i < vocab; i += SMP_THREADS) {
+          const float s = SHIFTED(i);
+          const unsigned int key = float_key(s);
+          if ((key & mask) != prefix) continue;
+          const float w = expf(s);
+          if (!survives(keep, key, i, w)) continue;
+          atomicAdd(&group_n[group * 256 + ((key >> shift) & 255u)], 1u);
+          atomicAdd(&group_m[group * 256 + ((key >> shift) & 255u)], (unsigned long long)(w * MASS_SCALE));
         }
       }
       if (shift == 24) {
         unsigned long long total;
         block_exclusive_scan<unsigned long long>(local_total, scan_u, &total);
         limit = (unsigned long long)((double)p * (double)total);
+      }
+      __syncthreads();
+      if (tid < 256) {
+        unsigned int total_n = 0u;
+        unsigned long long total_m = 0ull;
+        for (int w = 0; w < SMP_GROUPS; ++w) { total_n += group_n[w * 256 + tid]; total_m += group_m[w * 256 + tid]; }
+        hist_n[tid] = total_n;
+        hist_m[tid] = total_m;
       }
       __syncthreads();
       if (tid == 0) {
