@@ -387,6 +387,38 @@ def test_sampling_matches_filtered_distribution(native, temperature, top_k, top_
         assert set(got) == {int(base.argmax())}
 
 
+@pytest.mark.parametrize("temperature,top_k,top_p,min_p", [(0.9, None, 1.0, 0.0), (1.0, 30, 1.0, 0.0), (1.1, None, 0.8, 0.0),
+                                                           (0.8, 50, 0.9, 0.01)])
+def test_sampling_large_vocabulary_over_a_cluster(native, temperature, top_k, top_p, min_p) -> None:
+    """A vocabulary large enough that a row is cut over the blocks of a cluster: same draws
+    as the plain filter."""
+    vocab, rows = 70001, 12
+    g = torch.Generator().manual_seed(21)
+    base = torch.randn(vocab, generator=g) * 2.5
+    logits = base[None].repeat(rows, 1).contiguous()
+    seeds = torch.arange(rows, dtype=torch.int64) * 104729 + 3
+    counters = torch.arange(rows, dtype=torch.int64) * 5
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    status = status_word()
+    native.sample(
+        logits.to(DEV), out, status,
+        temperature=torch.full((rows,), temperature, device=DEV),
+        top_k=torch.full((rows,), top_k or 0, dtype=torch.int32, device=DEV),
+        top_p=torch.full((rows,), top_p, device=DEV), min_p=torch.full((rows,), min_p, device=DEV),
+        seeds=seeds.to(DEV), counters=counters.to(DEV),
+    )
+    assert int(status.item()) == 0
+    got = out.cpu().tolist()
+    filtered = plain.filter_logits(base[None], temperature, top_k, top_p, min_p)[0]
+    survivors = set(torch.nonzero(torch.isfinite(filtered)).flatten().tolist())
+    assert set(got) <= survivors
+    for r in range(rows):
+        want, running, target = twin_draw(base, temperature, top_k, top_p, min_p, int(seeds[r]), int(counters[r]))
+        if got[r] != want:
+            gap = float((running - target).abs().min())
+            assert gap < 1e-5 * float(running[-1]), (r, got[r], want, gap)
+
+
 def test_sampling_rows_are_independent(native) -> None:
     """Different parameters per row in one launch; greedy rows beside sampled ones."""
     vocab = 1000
