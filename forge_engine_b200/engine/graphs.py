@@ -67,20 +67,20 @@ class DecodeGraphs:
     def usable(self) -> bool:
         return all(getattr(block.mixer, "graph_safe", False) for block in self.model.blocks)
 
-    def _plan(self, entries, bucket_entries: int, width: int) -> BatchPlan:
+    def _plan(self, entries, bucket_entries: int, width: int, spread: int = 1) -> BatchPlan:
         return plan_batch(entries, self.cache, pad_entries=bucket_entries - len(entries), table_width=width,
                           null_page=self.cache.null_page)
 
     def _capture(self, key: tuple) -> _CapturedStep:
-        bucket_entries, width = key
+        bucket_entries, width, spread = key
         device = self.model.ctx.device
         page = self.cache.page_size
         # A batch of filler entries only: it has the bucket's layout and is safe to run.
         plan = self._plan([], bucket_entries, width)
-        # The capture sees host-side entries that all sit at the bucket's longest context,
-        # so that size decisions made on the host (attention splits) fit every step that
-        # will be replayed with this graph.
-        plan.entries = [(0, width * page - 1, 1)] * bucket_entries
+        # The capture sees host-side entries that stand for every step that will be replayed
+        # with this graph, so that size decisions made on the host (attention splits) fit
+        # them: one entry at the bucket's longest context, the others `spread` times shorter.
+        plan.entries = [(0, width * page - 1, 1)] + [(0, max(1, width * page // spread) - 1, 1)] * (bucket_entries - 1)
         plan.max_ctx = width * page
         buffer = torch.tensor(plan.flat, dtype=torch.int32).to(device)
         batch = batch_from_buffer(plan, buffer)
@@ -109,7 +109,12 @@ class DecodeGraphs:
             (len(self.cache.request(e.key).tables[g].pages) for e in entries for g in range(len(self.cache.groups))),
             default=1,
         )
-        key = (bucket_entries, _bucket(widest, 8))
+        # how much longer the longest context is than the average one (a power of two, rounded down)
+        pages = [max(len(t.pages) for t in self.cache.request(e.key).tables) for e in entries]
+        spread = 1
+        while spread < 32 and widest * len(pages) >= 2 * spread * max(1, sum(pages)):
+            spread *= 2
+        key = (bucket_entries, _bucket(widest, 8), spread)
         # every entry is laid out as wanting its token, so that the layout is fixed
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         full = [type(e)(e.key, e.tokens, [0]) for e in entries]

@@ -9,6 +9,7 @@ head_dim, window) between steps.
 
 from __future__ import annotations
 
+import functools
 import os
 
 import torch
@@ -29,25 +30,62 @@ FUSED_PROJECTION_ROWS = 16
 CLUSTER_SPLITS = 8            # this many blocks combine their results inside a cluster
 CLUSTER_WORTH_TILES = 96      # from here on (6,144 keys) more than one cluster per pair pays
 
+# Costs in units of one 64-key tile of one block (about 1.4 us), from measurements of the
+# split decode kernel on a B200: combining the splits inside a cluster, through global
+# memory, and what every round of blocks over the machine's slots costs beside its tiles.
+MERGE_IN_CLUSTER, MERGE_THROUGH_MEMORY, ROUND_OVERHEAD = 2, 9, 3
 
-def choose_splits(pairs: int, tiles: int) -> int:
-    """How many blocks share one (request, kv head)'s keys.
 
-    Few pairs: fill the machine's slots once, every block getting at least four 64-key
-    tiles.  With more pairs than half the slots the machine is full anyway and splitting
-    only adds partial results to combine (measured: one split is fastest at 512 pairs of
-    2,048 keys; very long contexts take two).  Up to 8 blocks combine their partial results
-    through shared memory; beyond that clusters of 8 do, and the clusters' results go through
-    global memory and a last-arriver merge - worth it from about 6,000 keys on (measured for
-    one request: 8,192 keys 22.9 us with 8 splits, 17.3 us with 32; 2,048 keys 7.7 against
-    10.8 us with 16)."""
+def choose_splits(tile_counts, kv_heads: int) -> int:
+    """How many blocks share one (request, kv head)'s keys; ``tile_counts`` are the 64-key
+    tiles of the step's requests.  Every request gets the same number of splits."""
+    return _choose_splits(tuple(sorted(max(1, int(t)) for t in tile_counts)), int(kv_heads))
+
+
+def _even_splits(pairs: int, tiles: int) -> int:
+    """Requests of about the same length (measured on a B200, 8 kv heads, head size 128).
+    Few pairs: fill the machine's slots once, every block getting at least four tiles; up to 8
+    blocks combine inside a cluster, and going beyond (clusters of 8 whose results pass through
+    memory) pays from about 6,000 keys on (one request: 8,192 keys 22.9 us with 8 splits,
+    17.3 us with 32; 2,048 keys 7.7 against 10.8 us with 16).  With more pairs than half the
+    slots the machine is full anyway: one split up to 4,096 keys (512 pairs of 2,048 keys:
+    100 us against 116 us with two), two beyond.  Clusters of 3, 5, 6 or 7 blocks measured
+    badly (12 requests: 38.8 us with 3 splits, 28.3 us with 2), so counts are powers of two."""
     most = max(1, min(MAX_SPLITS, tiles // 4))
     if pairs * 2 > DECODE_SLOTS:
         return 1 if tiles <= 64 else min(most, 2)
     splits = max(1, min(most, DECODE_SLOTS // pairs))
     if splits > CLUSTER_SPLITS:
-        splits = CLUSTER_SPLITS if tiles < CLUSTER_WORTH_TILES else splits - splits % CLUSTER_SPLITS
-    return splits
+        return CLUSTER_SPLITS if tiles < CLUSTER_WORTH_TILES else splits - splits % CLUSTER_SPLITS
+    return 1 << (splits.bit_length() - 1)
+
+
+@functools.lru_cache(maxsize=4096)
+def _choose_splits(tile_counts: tuple, kv_heads: int) -> int:
+    pairs = len(tile_counts) * kv_heads
+    longest = tile_counts[-1]
+    median = tile_counts[len(tile_counts) // 2]
+    if longest < 2 * median:
+        return _even_splits(pairs, longest)
+    # One request much longer than most: it decides how long its blocks run, while all blocks
+    # together pass through the machine's slots, in rounds if they are more.  Estimate for s
+    # splits, in tiles of one block: max(longest / s, all tiles / slots, rounds x the median
+    # block) + the cost of combining + an overhead per round; the cheapest wins.  Measured:
+    # one request of 32,768 keys beside seven of 2,048: 176 us with the 4 splits of even
+    # requests, 94-102 us with 16-32; one of 16,384 beside 31 of 1,024: 329 us with 1, 108 us
+    # with 8; one of 8,192 beside 63 of 2,048: 219 us with 1, 171 us with 2, 147 us with 4.
+    total = sum(tile_counts) * kv_heads
+    best, best_cost = 1, None
+    for splits in (1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64):
+        if splits > 1 and (longest // splits < 2 or splits > MAX_SPLITS):
+            break
+        rounds = -(-pairs * splits // DECODE_SLOTS)
+        merge = 0 if splits == 1 else (MERGE_IN_CLUSTER if splits <= CLUSTER_SPLITS else MERGE_THROUGH_MEMORY)
+        tiles = max(-(-longest // splits), -(-total // DECODE_SLOTS), rounds * -(-median // splits))
+        cost = tiles + merge + ROUND_OVERHEAD * rounds
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
+    return best
 
 
 class GQAttention(Mixer):
@@ -158,12 +196,10 @@ class GQAttention(Mixer):
         run_prefill = len(small) < batch.n_entries
         splits = 1
         if run_decode:
-            longest = max(start + count for start, count in small)
+            contexts = [start + count for start, count in small]
             if self.spec.window:
-                longest = min(longest, self.spec.window + limit)
-            tiles = -(-longest // 64)
-            pairs = len(small) * self.nkv
-            splits = choose_splits(pairs, tiles)
+                contexts = [min(c, self.spec.window + limit) for c in contexts]
+            splits = choose_splits([-(-c // 64) for c in contexts], self.nkv)
         native.attention_mma(
             qkv, qkv.shape[1], k_cache, v_cache, table, batch.cu_tokens, batch.starts,
             batch.n_entries, batch.max_new, self.spec.window, self.spec.scale, out, self.nq,

@@ -219,3 +219,25 @@ def test_windowed_group_reserves_less() -> None:
     s.run_until_idle()
     assert s.request(rid).status is RequestStatus.FINISHED
     assert runner.cache.leased_pages() == [0]
+
+
+def test_decode_split_choice() -> None:
+    """The number of blocks per (request, kv head) in split decode attention: the measured
+    rule for requests of even length, more splits when one request is much longer."""
+    from forge_engine_b200.parts.attention import choose_splits
+
+    assert choose_splits([33] * 8, 8) == 4          # 8 requests of 2,048 keys: 256 blocks fill the slots once
+    assert choose_splits([33] * 64, 8) == 1         # the machine is full anyway
+    assert choose_splits([128] * 64, 8) == 2        # ... but long contexts take two
+    assert choose_splits([33], 8) == 8              # one request: a cluster of 8
+    assert choose_splits([513], 8) == 32            # one long request: clusters of 8 through memory
+    assert choose_splits([3] * 8, 8) == 1           # too short to split
+    for counts in ([33] * 12, [33] * 3, [100] * 5, [513] + [33] * 7, [257] + [17] * 31, [129] + [33] * 63):
+        splits = choose_splits(counts, 8)
+        assert splits in (1, 2, 4, 8) or (splits % 8 == 0 and splits <= 64)
+        assert max(counts) // splits >= 2 or splits == 1
+    # one long request beside short ones gets more splits than the short ones alone would
+    assert choose_splits([513] + [33] * 7, 8) > choose_splits([33] * 8, 8)
+    assert choose_splits([257] + [17] * 31, 8) > choose_splits([17] * 32, 8)
+    # the order of the requests does not matter
+    assert choose_splits([33] * 7 + [513], 8) == choose_splits([513] + [33] * 7, 8)
