@@ -183,7 +183,8 @@ class GQAttention(Mixer):
         """Whether the q/k/v projection's epilogue can do the per-head norms, the rotation
         and the page write: the tcgen05 kernel takes the call, a head is one 128-feature
         tile, and the whole head is rotated."""
-        return (self.d == 128 and rotary is not None and rotary[1] == 128 and k_cache.dtype == torch.bfloat16
+        return (self.d == 128 and rotary is not None and rotary[1] == 128 and hasattr(self.position, "table")
+                and k_cache.dtype == torch.bfloat16
                 and x.shape[0] <= FUSED_PROJECTION_ROWS and self.qkv_proj._tc5_ok(x)
                 and os.environ.get("FORGE_ENGINE_FUSED_QKV", "1") != "0")
 
