@@ -78,7 +78,9 @@ class Norm(Part):
 class PositionEncoding(Part):
     """Either gives the fused q/k kernel a rotary table (``rotary()`` returns
     ``(inv_freq float32[rotary_dim/2], rotary_dim)``) or returns None there and rewrites
-    q and k itself in ``apply(qkv, num_q_heads, num_kv_heads, head_dim, batch)``."""
+    q and k itself in ``apply(qkv, num_q_heads, num_kv_heads, head_dim, batch)``.  A rotary
+    part may also offer ``table(batch)``: cosine and sine of the step's angles
+    [tokens, rotary_dim/2, 2], taken once per step and shared by all layers."""
 
     def rotary(self):
         return None
