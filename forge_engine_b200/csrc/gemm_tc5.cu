@@ -465,6 +465,63 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
       for (int peer = 0; peer < 8; ++peer)
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[peer]) : "r"(local), "r"(peer < p.ksplit ? peer : 0));
+      constexpr bool PLAIN_STORE = EPI == EPI_STORE_BF16 || EPI == EPI_STORE_F32 || EPI == EPI_ADD_F32;
+      if (PLAIN_STORE && (p.o & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0) {
+        // A warp takes a token and a lane four neighbouring features: one 16-byte load per
+        // block of the cluster instead of four 4-byte ones (the loads between SMs are what
+        // this phase waits for), two tokens in flight, and the residual row fetched first.
+        const int f4 = m0 + lane * 4;
+        const bool inside = f4 < p.o;
+        for (int t = t_begin + quarter; t < t_end; t += 8) {
+          float4 prior[2], part[2][8];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int tok = t + 4 * u;
+            prior[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (EPI == EPI_ADD_F32 && inside && tok < t_end)
+              prior[u] = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.y) +
+                                                                (size_t)(n0 + tok) * p.o + f4));
+          }
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int tok = t + 4 * u;
+#pragma unroll
+            for (int peer = 0; peer < 8; ++peer) {
+              part[u][peer] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (peer < p.ksplit && tok < t_end)
+                asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+                             : "=f"(part[u][peer].x), "=f"(part[u][peer].y), "=f"(part[u][peer].z), "=f"(part[u][peer].w)
+                             : "r"(remote[peer] + (unsigned)((tok * BM + lane * 4) * 4)) : "memory");
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int tok = t + 4 * u;
+            if (tok >= t_end || !inside) continue;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int peer = 0; peer < 8; ++peer) {
+              v.x += part[u][peer].x; v.y += part[u][peer].y; v.z += part[u][peer].z; v.w += part[u][peer].w;
+            }
+            if (p.bias) {
+              v.x += p.bias[f4]; v.y += p.bias[f4 + 1]; v.z += p.bias[f4 + 2]; v.w += p.bias[f4 + 3];
+            }
+            const size_t at = (size_t)(n0 + tok) * p.o + f4;
+            if (EPI == EPI_STORE_BF16) {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+              uint2 packed;
+              packed.x = *reinterpret_cast<unsigned*>(&lo);
+              packed.y = *reinterpret_cast<unsigned*>(&hi);
+              *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.y) + at) = packed;
+            } else if (EPI == EPI_STORE_F32) {
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + at) = v;
+            } else {
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + at) =
+                  make_float4(prior[u].x + v.x, prior[u].y + v.y, prior[u].z + v.z, prior[u].w + v.w);
+            }
+          }
+        }
+      } else
       // four tokens at a time, so that their loads from the other blocks are in flight together
       for (int t = t_begin; t < t_end; t += 4) {
         float part[4][8];
