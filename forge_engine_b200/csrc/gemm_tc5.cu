@@ -15,9 +15,10 @@
 //                             residual add, coalesced stores along the feature dimension
 //   grid (feature tiles, token tiles, k-splits).  With k-splits > 1 the blocks of one tile
 //   add their partial tiles in split order, so results do not depend on timing: up to 8
-//   splits form a thread-block cluster and its first block reads the others' partial tiles
-//   from their shared memory; beyond that (or for wide token tiles) partial tiles go
-//   through a workspace and the block that arrives last adds them.
+//   splits form a thread-block cluster whose blocks each finish a share of the tile's
+//   tokens, reading the others' partial tiles from their shared memory; beyond that (or for
+//   wide token tiles) partial tiles go through a workspace and the block that arrives last
+//   adds them.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the block sets a bit in the
 // status word, stops issuing work, frees its tensor memory and returns.
@@ -383,8 +384,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       }
     } else if (ok && p.cluster_reduce) {
       // stash the partial tile in this block's shared memory ([token][feature], over the
-      // first weight stages, which nobody reads any more); the cluster's first block adds
-      // the stashes below
+      // first weight stages, which nobody reads any more); the cluster's blocks add the
+      // stashes below
       float* stash = reinterpret_cast<float*>(a_tiles);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
