@@ -983,10 +983,29 @@ const CUtensorMap* cache_map(const void* base, int rows, int page_size, bool lin
 }  // namespace
 
 #include "attention_tc5.cuh"
+#include "attention_balanced.cuh"
 
 // Workspace sizes (in floats) the decode path needs for `entries` and `num_splits`.
 FE_EXPORT long long SYM(fe_attn_workspace_floats_d)(int entries, int num_kv_heads, int num_splits) {
   return (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
+}
+
+// Blocks of the balanced decode kernel: as many as the GPU holds at once (0: it cannot run).
+// Its workspace holds 2 * blocks * 16 * (D + 2) floats.
+FE_EXPORT int SYM(fe_attn_balanced_blocks_d)() {
+  static int blocks = -1;
+  if (blocks < 0) {
+    blocks = 0;
+    int device = 0, sms = 0, per_sm = 0;
+    if ((D % 64) == 0 && ensure_encode() && cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess &&
+        cudaFuncSetAttribute(attn_decode_balanced_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)DECODE_BALANCED_SMEM) == cudaSuccess &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_balanced_kernel, TMA_THREADS,
+                                                      DECODE_BALANCED_SMEM) == cudaSuccess)
+      blocks = sms * per_sm < BAL_MAX_BLOCKS ? sms * per_sm : BAL_MAX_BLOCKS;
+  }
+  return blocks;
 }
 
 // `counters` (one zeroed unsigned per entry and kv head, left zeroed) lets the decode
@@ -1001,7 +1020,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
                                       int total_tokens, int window, float scale, int mode, int num_splits,
                                       float* workspace, unsigned* counters, int* status, cudaStream_t stream) {
   if (entries <= 0) return 0;
-  if (groups < 1 || groups > DEC_ROWS || num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return FE_ERR_BAD_SHAPE;
+  if (groups < 1 || groups > DEC_ROWS || num_splits < 0 || num_splits > MERGE_MAX_SPLITS) return FE_ERR_BAD_SHAPE;
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return FE_ERR_BAD_ALIGN;
   if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
@@ -1058,6 +1077,25 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
         if (rc) return rc;
       }
     }
+  }
+  if (use_decode && num_splits == 0) {
+    // the step's tiles spread evenly over as many blocks as the GPU holds at once
+    if (workspace == nullptr || entries > BAL_MAX_ENTRIES) return FE_ERR_BAD_SHAPE;
+    if ((D % 64) != 0 || page_size > BN || (BN % page_size) != 0) return FE_ERR_BAD_SHAPE;
+    const CUtensorMap* mk = cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size, true);
+    const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size, true) : nullptr;
+    if (!mk || !mv) return FE_ERR_BAD_SHAPE;
+    const int blocks = SYM(fe_attn_balanced_blocks_d)();
+    if (blocks <= 0) return FE_ERR_BAD_SHAPE;
+    p.row_lo = 0; p.row_hi = DEC_ROWS;
+    p.ws_ml = workspace + (size_t)2 * blocks * DEC_ROWS * D;
+    int rc = fe_launch_dependent(attn_decode_balanced_kernel, dim3(blocks), dim3(TMA_THREADS), DECODE_BALANCED_SMEM,
+                                 stream, *mk, *mv, p, entries);
+    if (rc) return rc;
+    rc = fe_launch_dependent(attn_merge_balanced_kernel, dim3(entries, num_kv_heads), dim3(THREADS), 0, stream, p,
+                             entries, blocks);
+    if (rc) return rc;
+    return fe_last_error();
   }
   if (use_decode) {
     if (num_splits > 1 && workspace == nullptr) return FE_ERR_BAD_SHAPE;

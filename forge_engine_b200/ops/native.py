@@ -75,6 +75,7 @@ def _declare(handle: ctypes.CDLL) -> None:
 
 
 _attention_libs: dict = {}
+_attention_handles: dict = {}
 
 
 def attention_lib(head_dim: int):
@@ -91,6 +92,7 @@ def attention_lib(head_dim: int):
         fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, i, f, i, i, p, p, p, p]
         fn.restype = c_int
         _attention_libs[head_dim] = fn
+        _attention_handles[head_dim] = handle
     return fn
 
 
@@ -283,6 +285,21 @@ def attention_simt(
     )
 
 
+_balanced_blocks: dict = {}
+
+
+def attention_balanced_blocks(head_dim: int) -> int:
+    """Blocks the balanced decode kernel of this head size runs with (0: it cannot run)."""
+    blocks = _balanced_blocks.get(head_dim)
+    if blocks is None:
+        attention_lib(head_dim)
+        fn = getattr(_attention_handles[head_dim], f"fe_attn_balanced_blocks_d{head_dim}")
+        fn.restype = c_int
+        fn.argtypes = []
+        blocks = _balanced_blocks[head_dim] = int(fn())
+    return blocks
+
+
 _attn_counters: dict = {}
 
 
@@ -320,13 +337,20 @@ def attention_mma(
 ) -> None:
     """Tensor-core paged attention (bfloat16).  Entries with more than 16 rows (new
     tokens x heads per kv head) go to the prefill kernel, the others to the split
-    decode kernel; ``run_prefill`` / ``run_decode`` say which kinds the batch holds."""
+    decode kernel; ``run_prefill`` / ``run_decode`` say which kinds the batch holds.
+    ``num_splits`` blocks share a request's keys; 0 spreads the key tiles of all decode
+    entries evenly over as many blocks as the GPU holds at once."""
     num_pages, nkv, page_size, head_dim = k_cache.shape
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     groups = num_q_heads // nkv
     mode = (1 if run_prefill else 0) | (2 if run_decode else 0)
     workspace = counters = None
-    if run_decode and num_splits > 1:
+    if run_decode and num_splits == 0:
+        blocks = attention_balanced_blocks(head_dim)
+        if blocks <= 0:
+            raise UnsupportedShapeError(f"attention_mma: no balanced decode kernel for head size {head_dim}")
+        workspace = torch.empty(2 * blocks * ATTN_DECODE_ROWS * (head_dim + 2), dtype=torch.float32, device=q.device)
+    elif run_decode and num_splits > 1:
         floats = entries * nkv * num_splits * ATTN_DECODE_ROWS * (head_dim + 2)
         workspace = torch.empty(floats, dtype=torch.float32, device=q.device)
         if merge_in_kernel:

@@ -34,12 +34,17 @@ CLUSTER_WORTH_TILES = 96      # from here on (6,144 keys) more than one cluster 
 # split decode kernel on a B200: combining the splits inside a cluster, through global
 # memory, and what every round of blocks over the machine's slots costs beside its tiles.
 MERGE_IN_CLUSTER, MERGE_THROUGH_MEMORY, ROUND_OVERHEAD = 2, 9, 3
+SPLIT_TILE_US = 1.45
+BALANCED_BASE_US, BALANCED_TILE_US, BALANCED_PAIR_US, BALANCED_PIECE_US = 15.0, 0.0049, 0.003, 0.27
+BALANCED_MAX_ENTRIES = 256    # what the balanced kernel keeps in shared memory
 
 
-def choose_splits(tile_counts, kv_heads: int) -> int:
+def choose_splits(tile_counts, kv_heads: int, balanced: bool = False) -> int:
     """How many blocks share one (request, kv head)'s keys; ``tile_counts`` are the 64-key
-    tiles of the step's requests.  Every request gets the same number of splits."""
-    return _choose_splits(tuple(sorted(max(1, int(t)) for t in tile_counts)), int(kv_heads))
+    tiles of the step's requests.  Every request gets the same number of splits.  With
+    ``balanced`` the answer may be 0: the kernel that spreads all tiles evenly over the
+    machine's blocks is expected to be faster than any split."""
+    return _choose_splits(tuple(sorted(max(1, int(t)) for t in tile_counts)), int(kv_heads), bool(balanced))
 
 
 def _even_splits(pairs: int, tiles: int) -> int:
@@ -60,31 +65,55 @@ def _even_splits(pairs: int, tiles: int) -> int:
     return 1 << (splits.bit_length() - 1)
 
 
+def _split_cost(tile_counts: tuple, kv_heads: int, splits: int) -> int:
+    """Estimate for ``splits`` blocks per pair, in tiles of one block: the longest request
+    decides how long its blocks run, while all blocks together pass through the machine's
+    slots, in rounds if they are more: max(longest / s, all tiles / slots, rounds x the median
+    block) + the cost of combining + an overhead per round."""
+    pairs = len(tile_counts) * kv_heads
+    longest, median = tile_counts[-1], tile_counts[len(tile_counts) // 2]
+    total = sum(tile_counts) * kv_heads
+    rounds = -(-pairs * splits // DECODE_SLOTS)
+    merge = 0 if splits == 1 else (MERGE_IN_CLUSTER if splits <= CLUSTER_SPLITS else MERGE_THROUGH_MEMORY)
+    tiles = max(-(-longest // splits), -(-total // DECODE_SLOTS), rounds * -(-median // splits))
+    return tiles + merge + ROUND_OVERHEAD * rounds
+
+
 @functools.lru_cache(maxsize=4096)
-def _choose_splits(tile_counts: tuple, kv_heads: int) -> int:
+def _choose_splits(tile_counts: tuple, kv_heads: int, balanced: bool = False) -> int:
     pairs = len(tile_counts) * kv_heads
     longest = tile_counts[-1]
     median = tile_counts[len(tile_counts) // 2]
     if longest < 2 * median:
-        return _even_splits(pairs, longest)
-    # One request much longer than most: it decides how long its blocks run, while all blocks
-    # together pass through the machine's slots, in rounds if they are more.  Estimate for s
-    # splits, in tiles of one block: max(longest / s, all tiles / slots, rounds x the median
-    # block) + the cost of combining + an overhead per round; the cheapest wins.  Measured:
-    # one request of 32,768 keys beside seven of 2,048: 176 us with the 4 splits of even
-    # requests, 94-102 us with 16-32; one of 16,384 beside 31 of 1,024: 329 us with 1, 108 us
-    # with 8; one of 8,192 beside 63 of 2,048: 219 us with 1, 171 us with 2, 147 us with 4.
-    total = sum(tile_counts) * kv_heads
-    best, best_cost = 1, None
-    for splits in (1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64):
-        if splits > 1 and (longest // splits < 2 or splits > MAX_SPLITS):
-            break
-        rounds = -(-pairs * splits // DECODE_SLOTS)
-        merge = 0 if splits == 1 else (MERGE_IN_CLUSTER if splits <= CLUSTER_SPLITS else MERGE_THROUGH_MEMORY)
-        tiles = max(-(-longest // splits), -(-total // DECODE_SLOTS), rounds * -(-median // splits))
-        cost = tiles + merge + ROUND_OVERHEAD * rounds
-        if best_cost is None or cost < best_cost:
-            best, best_cost = splits, cost
+        best = _even_splits(pairs, longest)
+    else:
+        # One request much longer than most.  Measured: one request of 32,768 keys beside seven
+        # of 2,048: 176 us with the 4 splits of even requests, 94-102 us with 16-32; one of
+        # 16,384 beside 31 of 1,024: 329 us with 1, 108 us with 8; one of 8,192 beside 63 of
+        # 2,048: 219 us with 1, 171 us with 2, 147 us with 4.
+        best, best_cost = 1, None
+        for splits in (1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64):
+            if splits > 1 and (longest // splits < 2 or splits > MAX_SPLITS):
+                break
+            cost = _split_cost(tile_counts, kv_heads, splits)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = splits, cost
+    if balanced and len(tile_counts) <= BALANCED_MAX_ENTRIES:
+        # The balanced kernel (and the kernel that combines the pairs it cut) measured
+        # 15 us + 4.9 ns per tile + 3 ns per pair, whatever the lengths are (8 requests of 2,048
+        # keys 26 us, 64 of them 97 us, 200 of 300 keys 61 us); a tile of the split kernel's
+        # estimate is 1.45 us (32 requests of 2,048 keys: 35 tiles, 50 us measured).  The
+        # balanced kernel wins where blocks would run in two uneven rounds (40 requests of
+        # 3,000 keys: 134 -> 90 us) and wherever lengths differ much (one request of 32,768
+        # keys beside seven of 2,048: 96 -> 50 us; 64 requests of 16 to 4,096 keys: 139 -> 120 us).
+        # Combining costs by the pieces of the longest pair (one request of 8,192 keys is cut
+        # into 37 pieces per kv head: 31 us, against 17 us with 32 splits).
+        total = sum(tile_counts) * kv_heads
+        pieces = min(DECODE_SLOTS, longest * DECODE_SLOTS // total + 1)
+        balanced_us = (BALANCED_BASE_US + BALANCED_TILE_US * total + BALANCED_PAIR_US * pairs
+                       + BALANCED_PIECE_US * pieces)
+        if balanced_us < SPLIT_TILE_US * _split_cost(tile_counts, kv_heads, best):
+            return 0
     return best
 
 
@@ -200,7 +229,13 @@ class GQAttention(Mixer):
             contexts = [start + count for start, count in small]
             if self.spec.window:
                 contexts = [min(c, self.spec.window + limit) for c in contexts]
-            splits = choose_splits([-(-c // 64) for c in contexts], self.nkv)
+            # FORGE_ENGINE_DECODE_BALANCED: 0 never uses the balanced kernel, "always" uses it
+            # wherever it can run, anything else lets the estimate decide
+            wish = os.environ.get("FORGE_ENGINE_DECODE_BALANCED", "1")
+            balanced = (self.d % 64 == 0 and k_cache.shape[2] <= 64 and 64 % k_cache.shape[2] == 0
+                        and batch.n_entries <= BALANCED_MAX_ENTRIES and wish != "0")
+            splits = 0 if balanced and wish == "always" else choose_splits(
+                [-(-c // 64) for c in contexts], self.nkv, balanced)
         native.attention_mma(
             qkv, qkv.shape[1], k_cache, v_cache, table, batch.cu_tokens, batch.starts,
             batch.n_entries, batch.max_new, self.spec.window, self.spec.scale, out, self.nq,

@@ -93,6 +93,18 @@ def test_split_decode_long_contexts(native, splits) -> None:
     run_case(native, 32, 8, 128, 16, None, lengths, [1] * 6, splits, merge_in_kernel=False)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 2, 64, 64), (16, 1, 128, 4), (6, 3, 64, 8), (16, 1, 256, 32)])
+@pytest.mark.parametrize("window", [None, 500])
+def test_balanced_decode(native, nq, nkv, d, page, window) -> None:
+    """splits = 0: the key tiles of all decode entries spread evenly over the GPU's blocks.
+    Requests far longer than a block's share (cut into many pieces), shorter than it (several
+    pairs in one block), of one key, of a tile's exact length; prompt portions beside them."""
+    run_case(native, nq, nkv, d, page, window, [20000, 1, 777, 64, 65, 4000, 128, 9000], [1] * 8, 0)
+    run_case(native, nq, nkv, d, page, window, [3], [1], 0)
+    run_case(native, nq, nkv, d, page, window, [300, 5000, 200, 64, 2], [300, 1, 40, 1, 2], 0)
+    run_case(native, nq, nkv, d, page, window, [700] * 40 + [701, 1, 12000], [1] * 43, 0, sharp=True)
+
+
 def test_rows_do_not_depend_on_the_batch(native) -> None:
     """The prefill kernel gives the same bits for a request alone and beside others."""
     dtype = torch.bfloat16

@@ -207,6 +207,35 @@ def test_long_decoding(fe, dtype, tmp_path) -> None:
     assert runner.cache.leased_pages() == [0, 0]
 
 
+@pytest.mark.parametrize("graphs", [True, False])
+def test_decoding_with_the_balanced_attention_kernel(fe, tmp_path, monkeypatch, graphs) -> None:
+    """Requests of very different lengths decoded together with the kernel that spreads all
+    key tiles evenly over the blocks (forced here: tiny models never reach the sizes at which
+    it is chosen), one layer windowed, replayed from CUDA graphs and step by step."""
+    from forge_engine_b200.engine import StepEntry
+
+    from forge_engine_b200.engine import ModelRunner
+
+    monkeypatch.setenv("FORGE_ENGINE_DECODE_BALANCED", "always")
+    cfg, weights = make_model_folder(tmp_path / "model", plain.TINY_E, 7)
+    runner = ModelRunner.from_folder(tmp_path / "model", dtype="bfloat16", page_size=16, num_pages=80,
+                                     max_requests=4, use_graphs=graphs)
+    lengths = {"a": 330, "b": 3, "c": 140}
+    new = 72
+    ids = {k: random_ids(cfg.vocab_size, n + new, 20 + i) for i, (k, n) in enumerate(lengths.items())}
+    ref = {k: plain.forward_logits(v, weights, cfg) for k, v in ids.items()}
+    for k, n in lengths.items():
+        runner.begin(k)
+        runner.step([StepEntry(k, ids[k][:n], [])])
+    for i in range(new):
+        keys = [k for k in lengths if not (k == "b" and i % 3 == 2)]      # b sits some steps out
+        done = {k: lengths[k] + sum(1 for j in range(i) if not (k == "b" and j % 3 == 2)) for k in keys}
+        out = runner.step([StepEntry(k, [ids[k][done[k]]], [0]) for k in keys]).float().cpu()
+        for row, k in enumerate(keys):
+            torch.testing.assert_close(out[row], ref[k][done[k]], **bound("bfloat16", ref[k]))
+    runner.check_status()
+
+
 def test_pages_run_out_without_side_effects(fe, tmp_path) -> None:
     from forge_engine_b200.engine import StepEntry
     from forge_engine_b200.errors import KVCacheCapacityError

@@ -241,3 +241,15 @@ def test_decode_split_choice() -> None:
     assert choose_splits([257] + [17] * 31, 8) > choose_splits([17] * 32, 8)
     # the order of the requests does not matter
     assert choose_splits([33] * 7 + [513], 8) == choose_splits([513] + [33] * 7, 8)
+    # where the kernel that spreads the tiles evenly over the blocks may run (answer 0): uneven
+    # lengths and block counts that would need two uneven rounds go to it, what fills the
+    # slots once and single requests (many pieces to combine) stay with the splits
+    assert choose_splits([513] + [33] * 7, 8, balanced=True) == 0
+    assert choose_splits([257] + [17] * 31, 8, balanced=True) == 0
+    assert choose_splits([47] * 40, 8, balanced=True) == 0
+    assert choose_splits([32] * 64, 8, balanced=True) == 0
+    assert choose_splits([32] * 8, 8, balanced=True) == 4
+    assert choose_splits([32] * 32, 8, balanced=True) == 1
+    assert choose_splits([128], 8, balanced=True) == 32
+    assert choose_splits([32], 8, balanced=True) == 8
+    assert choose_splits([5] * 300, 8, balanced=True) == 1      # more entries than the kernel keeps on chip
