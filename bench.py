@@ -331,6 +331,75 @@ def kernel_shapes() -> int:
     return 0
 
 
+def decode_attention(spec: str) -> int:
+    """Decode attention alone at given context lengths, e.g. ``2048x64`` or ``32768x1,2048x7``
+    (length x requests): the split kernel with the split count the engine would pick, and the
+    kernel that spreads all key tiles evenly over the GPU's blocks.  32 query heads, 8 kv heads,
+    head size 128, pages of 16; 12 launches over 4 caches in a replayed CUDA graph, so that the
+    keys come from DRAM; CUDA events around the replay."""
+    import torch
+
+    from forge_engine_b200.ops import native
+    from forge_engine_b200.parts.attention import choose_splits
+
+    native.lib()
+    device = "cuda:0"
+    nq, nkv, d, page, layers, launches = 32, 8, 128, 16, 4, 12
+    contexts = []
+    for item in spec.split(","):
+        length, _, count = item.partition("x")
+        contexts += [int(length)] * int(count or 1)
+    batch = len(contexts)
+    pages_per = [-(-c // page) for c in contexts]
+    num_pages = sum(pages_per)
+    caches = [(torch.randn((num_pages, nkv, page, d), device=device).bfloat16(),
+               torch.randn((num_pages, nkv, page, d), device=device).bfloat16()) for _ in range(layers)]
+    order = torch.randperm(num_pages).to(torch.int32)
+    table = torch.full((batch, max(pages_per)), -1, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = order[at:at + n]
+        at += n
+    table = table.to(device)
+    q = torch.randn((batch, (nq + 2 * nkv) * d), device=device).bfloat16()
+    out = torch.empty((batch, nq * d), dtype=torch.bfloat16, device=device)
+    cu = torch.arange(batch + 1, dtype=torch.int32, device=device)
+    starts = torch.tensor([c - 1 for c in contexts], dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    kv_bytes = sum(contexts) * nkv * d * 2 * 2
+    tiles = [-(-c // 64) for c in contexts]
+    results = {"requests": batch, "longest": max(contexts), "tiles": sum(tiles) * nkv,
+               "picked": choose_splits(tiles, nkv, batch <= 256)}
+    for name, splits in (("split", choose_splits(tiles, nkv)), ("balanced", 0)):
+        if splits == 0 and batch > 256:
+            continue
+
+        def run(i):
+            k, v = caches[i % layers]
+            native.attention_mma(q, q.shape[1], k, v, table, cu, starts, batch, 1, None, d ** -0.5, out, nq, status,
+                                 False, True, splits)
+
+        for i in range(3):
+            run(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(launches):
+                run(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        us = begin.elapsed_time(end) / launches * 1e3
+        results[name] = {"splits": splits, "us": round(us, 1), "gb_per_s": round(kv_bytes / us / 1e3)}
+    assert int(status.item()) == 0
+    print(json.dumps({"metric": "decode attention alone", "impl": "ours", **results}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -345,6 +414,8 @@ def main() -> int:
                         help="time only the 2,048-token prefill (small cases for profiling)")
     parser.add_argument("--workload", choices=sorted(WORKLOADS),
                         help="instead of the decode benchmark: a whole workload through the scheduler")
+    parser.add_argument("--decode-attention", metavar="LENxN[,LENxN...]",
+                        help="instead: decode attention alone at these context lengths, split and balanced kernel")
     parser.add_argument("--kernels", action="store_true",
                         help="instead: this repository's kernels at the three kernel shapes upstream publishes")
     parser.add_argument("--kernel-times", action="store_true",
@@ -365,6 +436,8 @@ def main() -> int:
         return scheduler_workload(args.workload, args.layers)
     if args.kernels:
         return kernel_shapes()
+    if args.decode_attention:
+        return decode_attention(args.decode_attention)
 
     import torch
 
