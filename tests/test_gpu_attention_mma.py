@@ -56,7 +56,7 @@ def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, shar
 
 
 @pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 2, 64, 16), (6, 3, 48, 8), (4, 2, 16, 4),
-                                           (5, 1, 32, 16), (16, 1, 256, 32), (12, 4, 80, 16)])
+                                           (5, 1, 32, 16), (16, 1, 256, 32), (12, 4, 80, 16), (4, 2, 192, 16)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_prefill_and_decode_mixed(native, nq, nkv, d, page, window) -> None:
     # whole prompts, a portion that starts mid-page, single decoded tokens, a 2-token portion
@@ -93,7 +93,8 @@ def test_split_decode_long_contexts(native, splits) -> None:
     run_case(native, 32, 8, 128, 16, None, lengths, [1] * 6, splits, merge_in_kernel=False)
 
 
-@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 2, 64, 64), (16, 1, 128, 4), (6, 3, 64, 8), (16, 1, 256, 32)])
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 2, 64, 64), (16, 1, 128, 4), (6, 3, 64, 8), (16, 1, 256, 32),
+                                           (4, 2, 192, 16)])
 @pytest.mark.parametrize("window", [None, 500])
 def test_balanced_decode(native, nq, nkv, d, page, window) -> None:
     """splits = 0: the key tiles of all decode entries spread evenly over the GPU's blocks.
