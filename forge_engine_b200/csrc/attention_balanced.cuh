@@ -157,7 +157,7 @@ attn_decode_balanced_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   // the entries' lengths are the step's inputs, not the work of the kernel before this one
   bal_prefix(p, entries, in, tid, TMA_THREADS);
   const long long total = (long long)p.nkv * in.prefix[entries];
-  // with fewer tiles than blocks the first `total` blocks take one tile each: no block in
+  // with fewer units than blocks the first `total` blocks take one unit each: no block in
   // the middle of a pair may be without a piece, the merge counts on one from each
   const int blocks = (int)min((long long)gridDim.x, total);
   const bool idle = (int)blockIdx.x >= blocks;
