@@ -105,7 +105,7 @@ def _choose_splits(tile_counts: tuple, kv_heads: int, balanced: bool = False) ->
         # estimate is 1.45 us (32 requests of 2,048 keys: 35 tiles, 50 us measured).  The
         # balanced kernel wins where blocks would run in two uneven rounds (40 requests of
         # 3,000 keys: 134 -> 90 us) and wherever lengths differ much (one request of 32,768
-        # keys beside seven of 2,048: 96 -> 50 us; 64 requests of 16 to 4,096 keys: 139 -> 120 us).
+        # keys beside seven of 2,048: 96 -> 49 us; 64 requests of 16 to 4,096 keys: 140 -> 95 us).
         # Combining costs by the pieces of the longest pair (one request of 8,192 keys is cut
         # into 37 pieces per kv head: 31 us, against 17 us with 32 splits).
         total = sum(tile_counts) * kv_heads
