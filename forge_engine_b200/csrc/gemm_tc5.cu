@@ -33,6 +33,9 @@ constexpr int BK = 64;         // k per stage: 128 bytes of bfloat16 = one swizz
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr unsigned WAIT_LIMIT = 20000000u;
+// Widest token tile whose k-splits add up inside a cluster: the 32-bit partial tile of a
+// block (tokens x 128 features) must fit in its ring of stages (128 tokens: 64 of 96 KB).
+constexpr int CLUSTER_REDUCE_TOKENS = 128;
 
 enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3, EPI_QKV_ROPE = 4 };
 
@@ -271,6 +274,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   constexpr int STAGES = stages_for<BN>();
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static_assert(BN > CLUSTER_REDUCE_TOKENS || BN * BM * 4 <= STAGES * (A_BYTES + B_BYTES),
+                "a block's partial tile is stashed over its ring of stages");
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment: the swizzle pattern repeats every 8 rows of 128 bytes
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -639,13 +644,13 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
   const int kblocks = (k + BK - 1) / BK;
   if (ksplit > kblocks) ksplit = kblocks;
   const int bn = fe_gemm_tc5_tile(n);
-  if (ksplit > 1 && !(ksplit <= 8 && bn <= 64) && (ws_part == nullptr || ws_count == nullptr)) return FE_ERR_BAD_SHAPE;
+  if (ksplit > 1 && !(ksplit <= 8 && bn <= CLUSTER_REDUCE_TOKENS) && (ws_part == nullptr || ws_count == nullptr)) return FE_ERR_BAD_SHAPE;
   CUtensorMap mw, mx;
   int rc = make_map(&mw, w, o, k, BM);
   if (rc) return rc;
   rc = make_map(&mx, x, n, k, bn);
   if (rc) return rc;
-  const int cluster_reduce = (ksplit > 1 && ksplit <= 8 && bn <= 64) ? 1 : 0;
+  const int cluster_reduce = (ksplit > 1 && ksplit <= 8 && bn <= CLUSTER_REDUCE_TOKENS) ? 1 : 0;
   GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, ws_part, ws_count, status, rope ? *rope : QkvRope{}};
   dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
   if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;

@@ -448,7 +448,8 @@ def test_sampling_rows_are_independent(native) -> None:
 # ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("n,o,k,ksplit", [(1, 256, 128, 1), (8, 331, 72, 1), (5, 384, 200, 2), (33, 640, 2560, 4),
-                                            (64, 2560, 4096, 8), (100, 331, 72, 1), (300, 1000, 512, 2)])
+                                            (64, 2560, 4096, 8), (100, 331, 72, 1), (300, 1000, 512, 2), (128, 2560, 4096, 8),
+                                            (100, 640, 2560, 4), (70, 384, 9728, 3)])
 def test_gemm_tc5(native, n, o, k, ksplit) -> None:
     g = torch.Generator().manual_seed(n + o)
     x = torch.randn((n, k), generator=g).bfloat16().to(DEV)
@@ -540,7 +541,8 @@ def test_gemm_tc5_qkv_rope(native, n, nq, nkv, k, ksplit, norm, rotate) -> None:
     assert int(status.item()) == 0
 
 
-@pytest.mark.parametrize("n,inter,k,ksplit", [(3, 64, 96, 1), (24, 256, 256, 2), (64, 9728, 2560, 1)])
+@pytest.mark.parametrize("n,inter,k,ksplit", [(3, 64, 96, 1), (24, 256, 256, 2), (64, 9728, 2560, 1), (128, 9728, 2560, 1),
+                                              (90, 512, 640, 2)])
 def test_gemm_tc5_silu_mul(native, n, inter, k, ksplit) -> None:
     from forge_engine_b200.parts.linear import interleave_rows
 
