@@ -100,6 +100,9 @@ class CacheManager:
         self.device = device
         self.shares = dict(shares or {})
         self.null_page = num_pages
+        # one state row more than requests can hold: filler entries of fixed-size (replayed)
+        # batches read and write it, as their keys go to ``null_page``
+        self.null_slot = max_requests
         self.slots = StateSlots(max_requests)
         self.groups: list[LayerGroup] = []
         self._run_group: dict[int, tuple] = {}  # run -> (group index, unit slot)
@@ -145,7 +148,7 @@ class CacheManager:
             )
         for run, spec in self._state_specs.items():
             self._run_state[run] = torch.zeros(
-                (self.max_requests, *spec.shape), dtype=getattr(torch, spec.dtype), device=self.device
+                (self.max_requests + 1, *spec.shape), dtype=getattr(torch, spec.dtype), device=self.device
             )
 
     def bytes_per_token(self) -> int:
@@ -180,7 +183,8 @@ class CacheManager:
         )
 
     def state_of_run(self, run: int):
-        """State tensor [max_requests, *shape] of a run (or of the run it shares with)."""
+        """State tensor [max_requests + 1, *shape] of a run (or of the run it shares with);
+        the last row is the null slot of filler entries."""
         return self._run_state.get(self.shares.get(run, run))
 
     # -- requests ----------------------------------------------------------------

@@ -130,12 +130,11 @@ def run_generate(args: argparse.Namespace) -> int:
             import torch
 
             from .config import read_model_config
-            from .models import expected_tensors
             from .weights import random_tensors, write_model_folder
 
-            _, _, spec = read_model_config(raw)
+            arch, _, spec = read_model_config(raw)
             write_model_folder(args.save_model, raw,
-                               random_tensors(expected_tensors(spec), args.random_weights, dtype=torch.bfloat16))
+                               random_tensors(arch.expected_tensors(spec), args.random_weights, dtype=torch.bfloat16))
             engine = Engine.from_pretrained(args.save_model, engine_config=engine_config,
                                             scheduler_config=scheduler_config, device=args.device)
         else:

@@ -17,11 +17,38 @@ from .specs import ModelSpec
 
 @dataclass(frozen=True)
 class Architecture:
-    """``read(raw_dict) -> config`` and ``spec(config) -> ModelSpec`` of one architecture."""
+    """``read(raw_dict) -> config`` and ``spec(config) -> ModelSpec`` of one architecture.
+
+    ``assemble(spec, weights, ctx) -> model`` builds the model from tensors by checkpoint
+    name; left None, the decoder of ``models/decoder.py`` is built (embedding, the runs of
+    the schedule, final norm, output projection).  An architecture whose data flow differs
+    outside the blocks (a scaled embedding, capped logits, a second tower) brings its own:
+    any object with ``spec`` (vocab_size, max_positions, eos_token_ids), ``ctx``,
+    ``cache_needs() -> (needs per run, shares)`` and ``forward(batch, cache) -> logits``;
+    optionally ``graph_safe`` (decode steps may be captured and replayed) and
+    ``weight_bytes()``.  ``tensors(spec) -> {checkpoint name: WeightInfo}`` lists what
+    ``assemble`` needs; left None, the decoder's list is used.
+    """
 
     name: str
     read: Callable[[dict], object]
     spec: Callable[[object], ModelSpec]
+    assemble: Callable | None = None
+    tensors: Callable | None = None
+
+    def expected_tensors(self, spec) -> dict:
+        if self.tensors is not None:
+            return self.tensors(spec)
+        from ..models.decoder import expected_tensors
+
+        return expected_tensors(spec)
+
+    def build(self, spec, weights: dict, ctx):
+        if self.assemble is not None:
+            return self.assemble(spec, weights, ctx)
+        from ..models.decoder import DecoderModel
+
+        return DecoderModel(spec, weights, ctx)
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}

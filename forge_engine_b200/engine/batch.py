@@ -71,11 +71,12 @@ class BatchPlan:
 
 
 def plan_batch(entries: Sequence[StepEntry], cache, *, pad_entries: int = 0, table_width: int | None = None,
-               null_page: int | None = None) -> BatchPlan:
+               null_page: int | None = None, null_slot: int = 0) -> BatchPlan:
     """Lay out the step's integers.  Pages for the new tokens must already be reserved.
 
     ``pad_entries`` appends that many filler entries (one token at position 0 whose keys
-    go to ``null_page``, a page no request ever holds) so that the batch has a fixed
+    go to ``null_page``, a page no request ever holds, and whose state slot is
+    ``null_slot``, a row no request ever holds) so that the batch has a fixed
     number of entries; ``table_width`` fixes the width of every block table.  Both are
     used by replayed CUDA graphs, whose kernels are launched with fixed sizes."""
     token_ids: list[int] = []
@@ -109,7 +110,7 @@ def plan_batch(entries: Sequence[StepEntry], cache, *, pad_entries: int = 0, tab
         cu.append(cu[-1] + 1)
         starts.append(0)
         ctx_lens.append(1)
-        slots.append(0)
+        slots.append(null_slot)
     n, r = cu[-1], len(entries) + pad_entries
     tables = []
     for g in range(len(cache.groups)):

@@ -65,11 +65,13 @@ class DecodeGraphs:
         self.pool = None
 
     def usable(self) -> bool:
-        return all(getattr(block.mixer, "graph_safe", False) for block in self.model.blocks)
+        """The model says whether its steps can be captured (it asks its blocks, which ask
+        their parts); a model that does not say is run eagerly."""
+        return bool(getattr(self.model, "graph_safe", False))
 
     def _plan(self, entries, bucket_entries: int, width: int, spread: int = 1) -> BatchPlan:
         return plan_batch(entries, self.cache, pad_entries=bucket_entries - len(entries), table_width=width,
-                          null_page=self.cache.null_page)
+                          null_page=self.cache.null_page, null_slot=self.cache.null_slot)
 
     def _capture(self, key: tuple) -> _CapturedStep:
         bucket_entries, width, spread = key
@@ -110,7 +112,7 @@ class DecodeGraphs:
             default=1,
         )
         # how much longer the longest context is than the average one (a power of two, rounded down)
-        pages = [max(len(t.pages) for t in self.cache.request(e.key).tables) for e in entries]
+        pages = [max((len(t.pages) for t in self.cache.request(e.key).tables), default=0) for e in entries]
         spread = 1
         while spread < 32 and widest * len(pages) >= 2 * spread * max(1, sum(pages)):
             spread *= 2

@@ -14,11 +14,11 @@ import torch
 from ..cache.manager import CacheManager
 from ..config.registry import read_model_config
 from ..errors import ForgeEngineError, KVCacheCapacityError
-from ..models.decoder import DecoderModel, expected_tensors
+from ..models.decoder import DecoderModel
 from ..ops import native
 from ..parts.base import BuildContext
-from ..weights.loader import load_checkpoint
-from ..weights.random_init import random_tensors
+from ..weights.loader import open_checkpoint
+from ..weights.random_init import RandomTensors
 from .batch import StepBatch, StepEntry, build_batch
 from .graphs import DecodeGraphs
 
@@ -67,12 +67,15 @@ class ModelRunner:
         native.require_cuda()
         native.lib()
         engine_dtype = resolve_dtype(dtype)
-        _, _, spec = read_model_config(folder)
-        expected = expected_tensors(spec)
+        arch, _, spec = read_model_config(folder)
+        expected = arch.expected_tensors(spec)
         optional = (spec.head_name,) if spec.tie_embeddings else ()
-        weights = load_checkpoint(folder, expected, engine_dtype, device, optional)
+        # tensors reach the device when the model asks for them, layer by layer; what a part
+        # fuses (q/k/v rows, gate/up rows) never exists twice for more than one layer
+        weights = open_checkpoint(folder, expected, engine_dtype, device, optional)
         return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
-                                num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs)
+                                num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs,
+                                architecture=arch)
 
     @classmethod
     def from_random(cls, config: dict, seed: int, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
@@ -82,20 +85,30 @@ class ModelRunner:
         native.require_cuda()
         native.lib()
         engine_dtype = resolve_dtype(dtype)
-        _, _, spec = read_model_config(config)
-        weights = random_tensors(expected_tensors(spec), seed, std=std, dtype=engine_dtype, device=device)
+        arch, _, spec = read_model_config(config)
+        weights = RandomTensors(arch.expected_tensors(spec), seed, std=std, dtype=engine_dtype, device=device)
         return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
-                                num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs)
+                                num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs,
+                                architecture=arch)
 
     @classmethod
     def from_tensors(cls, spec, weights: dict, *, dtype, device, page_size: int, num_pages: int,
-                     max_requests: int, use_graphs: bool = True) -> "ModelRunner":
+                     max_requests: int, use_graphs: bool = True, architecture=None) -> "ModelRunner":
+        """``architecture`` (a registry entry) assembles the model; None builds the decoder of
+        ``models/decoder.py``."""
         native.require_cuda()
         native.lib()
         status = torch.zeros(1, dtype=torch.int32, device=device)
         ctx = BuildContext(dtype=resolve_dtype(dtype), device=torch.device(device), status=status)
         with torch.cuda.device(ctx.device):
-            model = DecoderModel(spec, weights, ctx)
+            try:
+                model = DecoderModel(spec, weights, ctx) if architecture is None else architecture.build(spec, weights, ctx)
+            except BaseException:
+                if hasattr(weights, "__exit__"):
+                    weights.__exit__(RuntimeError, None, None)
+                raise
+            if hasattr(weights, "close"):
+                weights.close()       # a lazily read checkpoint reports NaN and infinities here
             return cls(model, page_size=page_size, num_pages=num_pages, max_requests=max_requests,
                        use_graphs=use_graphs)
 

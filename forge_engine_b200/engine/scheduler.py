@@ -23,6 +23,7 @@ told), every request of that step fails and its pages and reservation are return
 from __future__ import annotations
 
 import random
+import time
 from collections import deque
 from dataclasses import dataclass, field
 from enum import Enum
@@ -83,6 +84,13 @@ class SchedulerSnapshot:
     allocated_blocks: tuple
     last_batch: tuple          # (request id, tokens in the step) in batch order
     last_batch_tokens: int
+    last_prefill_tokens: int = 0   # of the last step: tokens of prompt portions ...
+    last_decode_tokens: int = 0    # ... and decoded tokens fed back (one per decoding request)
+    last_step_ms: float = 0.0      # host wall time of the last ``step()`` call
+    model_steps: int = 0           # steps that ran the model, and what they ran, since the start
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    sampled_tokens: int = 0
 
 
 @dataclass
@@ -125,10 +133,17 @@ class Scheduler:
         default_params: SamplingParams | None = None,
         eos_token_ids: Sequence[int] = (),
         seed: int | None = None,
+        vocab_size: int | None = None,
+        max_positions: int | None = None,
     ) -> None:
+        """``vocab_size`` and ``max_positions`` bound what ``submit`` accepts; left None
+        they are read from ``runner.model.spec`` where the runner has a model."""
         self.runner = runner
         self.sampler = sampler
         self.config = config or SchedulerConfig()
+        spec = getattr(getattr(runner, "model", None), "spec", None)
+        self.vocab_size = vocab_size if vocab_size is not None else getattr(spec, "vocab_size", None)
+        self.max_positions = max_positions if max_positions is not None else getattr(spec, "max_positions", None)
         self.default_params = default_params or SamplingParams()
         self.eos_token_ids = frozenset(int(e) for e in eos_token_ids)
         cache = runner.cache
@@ -142,6 +157,9 @@ class Scheduler:
         self._next_number = 1
         self._iteration = 0
         self._last_batch: tuple = ()
+        self._last_split = (0, 0)      # (prompt tokens, decoded tokens) of the last step
+        self._last_step_ms = 0.0
+        self._totals = {"model_steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "sampled_tokens": 0}
         self._rng = random.Random(seed)
         # Decode steps can be launched one ahead: the next step takes its tokens from the
         # sampler's output on the device while the host is still reading the last ones, so
@@ -179,6 +197,18 @@ class Scheduler:
         if not prompt:
             raise ValueError("each request must contain one non-empty prompt")
         params = sampling_params or self.default_params
+        # What the step function would refuse is refused here, where it costs only this
+        # request: inside a step it would fail every request batched with it.
+        if self.vocab_size is not None:
+            bad = [t for t in prompt if not 0 <= t < self.vocab_size]
+            if bad:
+                raise ValueError(f"token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
+        # the last sampled token is never fed back, so the cache holds prompt + max_new - 1
+        if self.max_positions is not None and len(prompt) + params.max_new_tokens - 1 > self.max_positions:
+            raise ValueError(
+                f"prompt of {len(prompt)} tokens with max_new_tokens={params.max_new_tokens} "
+                f"exceeds max_position_embeddings={self.max_positions}"
+            )
         reservation = self.runner.cache.worst_case_pages(
             len(prompt) + params.max_new_tokens, self._max_portion()
         )
@@ -249,6 +279,20 @@ class Scheduler:
         """One scheduling iteration.  With look-ahead, a step of decoding requests only is
         launched before the tokens of the step before it have been read; its events are
         then those of the earlier step."""
+        began = time.perf_counter()
+        try:
+            return self._step()
+        finally:
+            self._last_step_ms = (time.perf_counter() - began) * 1e3
+
+    def _count(self, prefill: int, decode: int) -> None:
+        """Book the tokens of a step that is about to run the model."""
+        self._last_split = (prefill, decode)
+        self._totals["model_steps"] += 1
+        self._totals["prefill_tokens"] += prefill
+        self._totals["decode_tokens"] += decode
+
+    def _step(self) -> list:
         if self._inflight is not None:
             if all(r.status.terminal for r in self._inflight.requests):
                 self._inflight = None      # everything it decoded for has ended meanwhile
@@ -278,6 +322,7 @@ class Scheduler:
         ``previous`` the input tokens are that step's sampled ids, still on the device."""
         self._iteration += 1
         self._last_batch = tuple((r.request_id, 1) for r in requests)
+        self._count(0, len(requests))
         extra = 0 if previous is None else 1     # tokens sampled but not yet counted on the host
         try:
             if previous is None:
@@ -336,7 +381,10 @@ class Scheduler:
         self._last_batch = tuple((r.request_id, c) for r, c in selected)
         events: list[StreamEvent] = []
         if not selected:
+            self._last_split = (0, 0)
             return events
+        decoding = sum(r.status is RequestStatus.RUNNING for r, _ in selected)
+        self._count(sum(c for _, c in selected) - decoding, decoding)
         entries, sampling_rows = [], []
         for request, count in selected:
             if request.status is RequestStatus.RUNNING:
@@ -381,6 +429,7 @@ class Scheduler:
         """EOS -> "stop" (the EOS id is counted but not emitted); limit -> "length"
         (src/forge_engine/scheduler.py:472-519)."""
         request.pending_token = token
+        self._totals["sampled_tokens"] += 1
         reached_eos = token in request.eos_ids
         emitted: tuple = ()
         if reached_eos:
@@ -466,6 +515,10 @@ class Scheduler:
             allocated_blocks=tuple(self.runner.cache.leased_pages()),
             last_batch=self._last_batch,
             last_batch_tokens=sum(c for _, c in self._last_batch),
+            last_prefill_tokens=self._last_split[0],
+            last_decode_tokens=self._last_split[1],
+            last_step_ms=self._last_step_ms,
+            **self._totals,
         )
 
     def _request(self, request_id: str) -> _Request:

@@ -62,6 +62,12 @@ class DecoderModel:
             if run.cache_of is not None and not 0 <= run.cache_of < index:
                 raise ValueError(f"run {index} may only read the cache of an earlier run")
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model can be captured in a CUDA graph and replayed."""
+        return (all(getattr(block, "graph_safe", False) for block in self.blocks)
+                and getattr(self.final_norm, "graph_safe", False))
+
     # -- cache ---------------------------------------------------------------------
     def cache_needs(self) -> tuple:
         """(needs per run, {run: run whose cache it reads})."""

@@ -21,8 +21,9 @@ from .base import BuildContext, CacheView, Mixer, WeightInfo, build_part, regist
 from .linear import Linear, fuse_rows
 
 
-# Two blocks of the split decode kernel fit on an SM (148 SMs on a B200).
-DECODE_SLOTS = 296
+# Blocks of a decode kernel the GPU holds at once when nothing says otherwise (two per SM on
+# the 148 SMs of a B200); a mixer asks the kernel library for the figure of its device.
+DEFAULT_DECODE_SLOTS = 296
 MAX_SPLITS = 64   # what the merge takes
 # With more tokens a block of the projection finishes so many that the separate kernel is
 # faster (measured: 2.35 -> 2.27 ms per step at 1 token, no change at 8, 6.2 -> 6.7 ms at 64).
@@ -39,15 +40,17 @@ BALANCED_BASE_US, BALANCED_TILE_US, BALANCED_PAIR_US, BALANCED_PIECE_US = 15.0, 
 BALANCED_MAX_ENTRIES = 256    # what the balanced kernel keeps in shared memory
 
 
-def choose_splits(tile_counts, kv_heads: int, balanced: bool = False) -> int:
+def choose_splits(tile_counts, kv_heads: int, balanced: bool = False, slots: int = DEFAULT_DECODE_SLOTS) -> int:
     """How many blocks share one (request, kv head)'s keys; ``tile_counts`` are the 64-key
     tiles of the step's requests.  Every request gets the same number of splits.  With
     ``balanced`` the answer may be 0: the kernel that spreads all tiles evenly over the
-    machine's blocks is expected to be faster than any split."""
-    return _choose_splits(tuple(sorted(max(1, int(t)) for t in tile_counts)), int(kv_heads), bool(balanced))
+    machine's blocks is expected to be faster than any split.  ``slots``: blocks of the
+    decode kernels the GPU holds at once."""
+    return _choose_splits(tuple(sorted(max(1, int(t)) for t in tile_counts)), int(kv_heads), bool(balanced),
+                          max(1, int(slots)))
 
 
-def _even_splits(pairs: int, tiles: int) -> int:
+def _even_splits(pairs: int, tiles: int, DECODE_SLOTS: int) -> int:
     """Requests of about the same length (measured on a B200, 8 kv heads, head size 128).
     Few pairs: fill the machine's slots once, every block getting at least four tiles; up to 8
     blocks combine inside a cluster, and going beyond (clusters of 8 whose results pass through
@@ -65,7 +68,7 @@ def _even_splits(pairs: int, tiles: int) -> int:
     return 1 << (splits.bit_length() - 1)
 
 
-def _split_cost(tile_counts: tuple, kv_heads: int, splits: int) -> int:
+def _split_cost(tile_counts: tuple, kv_heads: int, splits: int, DECODE_SLOTS: int) -> int:
     """Estimate for ``splits`` blocks per pair, in tiles of one block: the longest request
     decides how long its blocks run, while all blocks together pass through the machine's
     slots, in rounds if they are more: max(longest / s, all tiles / slots, rounds x the median
@@ -80,12 +83,12 @@ def _split_cost(tile_counts: tuple, kv_heads: int, splits: int) -> int:
 
 
 @functools.lru_cache(maxsize=4096)
-def _choose_splits(tile_counts: tuple, kv_heads: int, balanced: bool = False) -> int:
+def _choose_splits(tile_counts: tuple, kv_heads: int, balanced: bool, DECODE_SLOTS: int) -> int:
     pairs = len(tile_counts) * kv_heads
     longest = tile_counts[-1]
     median = tile_counts[len(tile_counts) // 2]
     if longest < 2 * median:
-        best = _even_splits(pairs, longest)
+        best = _even_splits(pairs, longest, DECODE_SLOTS)
     else:
         # One request much longer than most.  Measured: one request of 32,768 keys beside seven
         # of 2,048: 176 us with the 4 splits of even requests, 94-102 us with 16-32; one of
@@ -95,7 +98,7 @@ def _choose_splits(tile_counts: tuple, kv_heads: int, balanced: bool = False) ->
         for splits in (1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64):
             if splits > 1 and (longest // splits < 2 or splits > MAX_SPLITS):
                 break
-            cost = _split_cost(tile_counts, kv_heads, splits)
+            cost = _split_cost(tile_counts, kv_heads, splits, DECODE_SLOTS)
             if best_cost is None or cost < best_cost:
                 best, best_cost = splits, cost
     if balanced and len(tile_counts) <= BALANCED_MAX_ENTRIES:
@@ -112,13 +115,16 @@ def _choose_splits(tile_counts: tuple, kv_heads: int, balanced: bool = False) ->
         pieces = min(DECODE_SLOTS, longest * DECODE_SLOTS // total + 1)
         balanced_us = (BALANCED_BASE_US + BALANCED_TILE_US * total + BALANCED_PAIR_US * pairs
                        + BALANCED_PIECE_US * pieces)
-        if balanced_us < SPLIT_TILE_US * _split_cost(tile_counts, kv_heads, best):
+        if balanced_us < SPLIT_TILE_US * _split_cost(tile_counts, kv_heads, best, DECODE_SLOTS):
             return 0
     return best
 
 
 class GQAttention(Mixer):
-    graph_safe = True
+    @property
+    def graph_safe(self) -> bool:
+        """The kernels here are; a position encoding that rewrites q and k itself decides."""
+        return bool(getattr(self.position, "graph_safe", False))
 
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         if spec.head_dim % 16 or spec.head_dim > 256:
@@ -145,6 +151,8 @@ class GQAttention(Mixer):
             self.q_norm = weights["q_norm.weight"].float().contiguous()
             self.k_norm = weights["k_norm.weight"].float().contiguous()
         self.position = build_part(spec.position, {}, ctx)
+        self._slots = None
+        self.last_splits = None   # what the last step's decode entries ran with (0: balanced kernel)
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
@@ -167,6 +175,17 @@ class GQAttention(Mixer):
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(kv=PagedKVSpec(self.nkv, self.d, self.spec.window))
+
+    def decode_slots(self) -> int:
+        """Blocks of the decode kernels this device holds at once: what the balanced kernel
+        of this head size is launched with (the library asks the occupancy of its own
+        kernel), else two per SM."""
+        if self._slots is None:
+            blocks = native.attention_balanced_blocks(self.d) if self.d % 64 == 0 else 0
+            if blocks <= 0:
+                blocks = 2 * torch.cuda.get_device_properties(self.ctx.device).multi_processor_count
+            self._slots = blocks
+        return self._slots
 
     def forward(self, x, batch, cache: CacheView):
         k_cache, v_cache = cache.kv
@@ -235,7 +254,8 @@ class GQAttention(Mixer):
             balanced = (self.d % 64 == 0 and k_cache.shape[2] <= 64 and 64 % k_cache.shape[2] == 0
                         and batch.n_entries <= BALANCED_MAX_ENTRIES and wish != "0")
             splits = 0 if balanced and wish == "always" else choose_splits(
-                [-(-c // 64) for c in contexts], self.nkv, balanced)
+                [-(-c // 64) for c in contexts], self.nkv, balanced, self.decode_slots())
+            self.last_splits = splits
         native.attention_mma(
             qkv, qkv.shape[1], k_cache, v_cache, table, batch.cu_tokens, batch.starts,
             batch.n_entries, batch.max_new, self.spec.window, self.spec.scale, out, self.nq,

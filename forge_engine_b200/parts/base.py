@@ -45,8 +45,8 @@ class CacheView:
 
     ``kv`` is ``(k_cache, v_cache)`` [pages, kv_heads, page_size, head_dim] or None;
     ``group`` indexes ``StepBatch.group_tables``; ``owns`` is False when the run reads
-    another run's cache and must not write; ``state`` is [max_requests, *shape] or None
-    and is indexed by ``StepBatch.slots``.
+    another run's cache and must not write; ``state`` is [max_requests + 1, *shape] or None
+    and is indexed by ``StepBatch.slots`` (the last row belongs to filler entries).
     """
 
     kv: tuple | None
@@ -57,6 +57,13 @@ class CacheView:
 
 class Part:
     """Common shape of all parts."""
+
+    # True if the part's work only launches kernels (or capturable torch ops) on the current
+    # stream and decides nothing from device data or from the host copy of the entries beyond
+    # their counts, so that a decode step can be captured once in a CUDA graph and replayed.
+    # A block is replayed only if all of its parts say so; parts defined elsewhere say no
+    # unless they set it.
+    graph_safe = False
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
@@ -96,10 +103,9 @@ class Mixer(Part):
     cache)`` gets the normalised activations [N, hidden] of all tokens of the step, the
     ``StepBatch`` and its ``CacheView``, and returns the update [N, hidden]."""
 
-    # True if ``forward`` only launches work on the current stream and decides nothing
-    # from device data or from the host copy of the entries beyond their counts, so that
-    # a decode step can be captured once in a CUDA graph and replayed.
-    graph_safe = False
+    # ``graph_safe`` (see Part): a mixer with state of its own must then index it with the
+    # device tensor ``batch.slots`` - filler entries of a replayed batch carry the cache's null
+    # slot, a row no request holds - and never with the host copy ``batch.entries``.
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds()

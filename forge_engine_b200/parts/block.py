@@ -29,6 +29,11 @@ class PreNormBlock:
     def cache_needs(self):
         return self.mixer.cache_needs()
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False)
+                   for part in (self.input_norm, self.mixer, self.post_norm, self.ffn))
+
     def forward(self, h, pending, batch, cache: CacheView):
         """``h`` 32-bit [N, hidden] (in place); ``pending`` the previous block's update or
         None.  Returns this block's feed-forward update, still to be added."""

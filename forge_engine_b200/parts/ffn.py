@@ -14,6 +14,8 @@ GATE_UP_BLOCK = 16
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         if spec.activation != "silu":
             raise ConfigError(f"activation {spec.activation!r} is not implemented (silu only)")

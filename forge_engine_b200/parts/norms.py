@@ -11,6 +11,8 @@ from .base import BuildContext, Norm, WeightInfo, register_part
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         self.size = spec.size
         self.eps = float(spec.eps)

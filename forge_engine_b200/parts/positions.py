@@ -14,6 +14,8 @@ from .base import BuildContext, PositionEncoding, register_part
 
 
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         if spec.rotary_dim % 2 or spec.rotary_dim > spec.head_dim:
             raise ValueError("rotary_dim must be even and at most head_dim")
@@ -38,6 +40,8 @@ class RotaryEncoding(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         pass
 

@@ -1,6 +1,7 @@
 """Checkpoint reading and seeded random weights."""
 
-from .loader import load_checkpoint
-from .random_init import random_tensors, write_model_folder
+from .loader import CheckpointTensors, load_checkpoint, open_checkpoint
+from .random_init import RandomTensors, random_tensors, write_model_folder
 
-__all__ = ["load_checkpoint", "random_tensors", "write_model_folder"]
+__all__ = ["CheckpointTensors", "RandomTensors", "load_checkpoint", "open_checkpoint", "random_tensors",
+           "write_model_folder"]

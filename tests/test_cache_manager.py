@@ -146,7 +146,8 @@ def test_state_slots_are_zeroed_on_lease() -> None:
     cache = CacheManager(needs, page_size=4, num_pages=4, max_requests=2, dtype=torch.float32, device="cpu")
     a = cache.begin_request("a")
     state = cache.state_of_run(0)
-    assert state.shape == (2, 3)
+    # one row more than requests: the null slot of fixed-size batches' filler entries
+    assert state.shape == (3, 3) and cache.null_slot == 2
     state[a.slot] += 5.0
     cache.end_request("a")
     b = cache.begin_request("b")

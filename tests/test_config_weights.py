@@ -189,3 +189,51 @@ def test_sharded_checkpoint_with_index(tmp_path) -> None:
     assert all(torch.equal(loaded[n], tensors[n]) for n in names)
     with pytest.raises(WeightsError, match="no safetensors"):
         load_checkpoint(tmp_path / "nowhere", expected, torch.bfloat16, "cpu")
+
+
+def test_values_that_are_not_finite_and_integer_matrices_are_refused(tmp_path) -> None:
+    """NaN and infinities are found while loading, with the tensors' names (upstream:
+    src/forge_engine/weights.py:238-241), and a matrix stored as integers is a wrong dtype."""
+    from forge_engine_b200.weights import open_checkpoint
+
+    _, _, spec = read_model_config(plain.TINY_A)
+    expected = expected_tensors(spec)
+    tensors = random_tensors(expected, seed=0)
+    tensors["model.layers.1.mlp.down_proj.weight"][3, 5] = float("nan")
+    tensors["model.layers.0.input_layernorm.weight"][2] = float("inf")
+    write_model_folder(tmp_path / "nan", plain.TINY_A, tensors)
+    with pytest.raises(WeightsError) as info:
+        load_checkpoint(tmp_path / "nan", expected, torch.bfloat16, "cpu")
+    text = str(info.value)
+    assert "NaN or infinity (2)" in text
+    assert "model.layers.1.mlp.down_proj.weight" in text and "model.layers.0.input_layernorm.weight" in text
+    assert "model.layers.0.mlp.down_proj.weight" not in text
+    # the lazy mapping reads on access, in any order, and keeps nothing
+    lazy = open_checkpoint(tmp_path / "nan", expected, torch.float32, "cpu")
+    names = list(lazy)
+    assert names == list(expected) and len(lazy) == len(expected)
+    last = lazy[names[-2]]
+    assert last.dtype == torch.float32 and torch.equal(last, tensors[names[-2]].float())
+    assert lazy[names[-2]] is not last
+    lazy.close()                                   # nothing bad was read: no error
+    with pytest.raises(KeyError):
+        lazy["not.a.tensor"]
+    good = random_tensors(expected, seed=0)
+    good["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(expected["model.layers.0.self_attn.q_proj.weight"].shape,
+                                                                 dtype=torch.int64)
+    write_model_folder(tmp_path / "int", plain.TINY_A, good)
+    with pytest.raises(WeightsError, match=r"wrong dtypes \(1\): model.layers.0.self_attn.q_proj.weight: stored as I64"):
+        load_checkpoint(tmp_path / "int", expected, torch.bfloat16, "cpu")
+
+
+def test_random_tensors_do_not_depend_on_the_order_they_are_drawn_in() -> None:
+    from forge_engine_b200.weights import RandomTensors
+
+    _, _, spec = read_model_config(plain.TINY_B)
+    expected = expected_tensors(spec)
+    eager = random_tensors(expected, seed=9, dtype=torch.float32)
+    lazy = RandomTensors(expected, 9, dtype=torch.float32)
+    for name in reversed(list(expected)):
+        assert torch.equal(lazy[name], eager[name])
+    a, b = "model.layers.0.mlp.gate_proj.weight", "model.layers.1.mlp.gate_proj.weight"
+    assert not torch.equal(eager[a], eager[b])

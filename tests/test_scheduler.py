@@ -86,8 +86,15 @@ def test_prompts_are_cut_under_the_token_budget_and_decodes_go_first() -> None:
     assert runner.batches[-1] == [("a", 1, (0,)), ("b", 5, (4,))]
     assert s.request(b).status is RequestStatus.RUNNING and s.request(b).fed_tokens == 17
     assert all(sum(n for _, n, _ in batch) <= 8 for batch in runner.batches)
+    snap = s.snapshot()
+    assert (snap.last_prefill_tokens, snap.last_decode_tokens, snap.last_batch_tokens) == (5, 1, 6)
+    assert (snap.model_steps, snap.prefill_tokens, snap.decode_tokens) == (4, 3 + 17, 3)
+    assert snap.sampled_tokens == 5 and snap.last_step_ms > 0.0
     s.run_until_idle()
-    assert s.snapshot().allocated_blocks == (0,)
+    snap = s.snapshot()
+    assert snap.allocated_blocks == (0,)
+    # every sampled token but the last of each request is fed back as one decoded token
+    assert snap.sampled_tokens == 8 and snap.decode_tokens == 6 and snap.prefill_tokens == 20
 
 
 def test_round_robin_and_max_batch_size() -> None:
@@ -253,3 +260,68 @@ def test_decode_split_choice() -> None:
     assert choose_splits([128], 8, balanced=True) == 32
     assert choose_splits([32], 8, balanced=True) == 8
     assert choose_splits([5] * 300, 8, balanced=True) == 1      # more entries than the kernel keeps on chip
+
+
+class StrictRunner(FakeRunner):
+    """Like the real step function it refuses a whole step for one bad token id or one
+    request beyond the position limit; it can also take a decode step's tokens from a
+    tensor, as a runner that replays captured steps does."""
+
+    supports_device_tokens = True
+
+    def __init__(self, max_positions=12, **kwargs):
+        from types import SimpleNamespace
+
+        super().__init__(**kwargs)
+        self.model = SimpleNamespace(spec=SimpleNamespace(vocab_size=VOCAB, max_positions=max_positions))
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            source, rows = device_tokens
+            entries = [type(e)(e.key, [int(source[r])], e.want) for e, r in zip(entries, rows)]
+        for e in entries:
+            if any(not 0 <= int(t) < VOCAB for t in e.tokens):
+                raise ValueError("token id outside the vocabulary")
+            if self.cache.request(e.key).length + len(e.tokens) > self.model.spec.max_positions:
+                raise RuntimeError("would exceed max_position_embeddings")
+        return super().step(entries)
+
+
+class AsyncArgmaxSampler(ArgmaxSampler):
+    class _Done:
+        def synchronize(self):
+            pass
+
+    def sample_async(self, logits, params, seeds, counters):
+        ids = logits.argmax(-1).to(torch.int32)
+        return ids, ids.clone(), self._Done()
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_one_bad_request_is_refused_alone(lookahead) -> None:
+    """A prompt with an id outside the vocabulary, or one that would pass the position
+    limit while decoding, is refused at submit; the requests beside it finish."""
+    config = SchedulerConfig(block_size=4, block_capacity=16, lookahead=lookahead)
+    runner = StrictRunner(max_positions=12)
+    s = Scheduler(runner, AsyncArgmaxSampler(), config, SamplingParams(max_new_tokens=4), seed=0)
+    assert s.lookahead is lookahead
+    good = [s.submit([1, 2, 3], request_id="a"), s.submit([9], request_id="b")]
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        s.submit([1, VOCAB, 2], request_id="bad-id")
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        s.submit([-1], request_id="negative")
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        s.submit(list(range(10)), request_id="too-long")          # 10 + 4 - 1 = 13 > 12
+    s.step()
+    # joins while the others decode; 9 + 4 - 1 = 12 positions is exactly the limit
+    good.append(s.submit(list(range(9)), request_id="c"))
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        s.submit(list(range(9)), request_id="d", sampling_params=SamplingParams(max_new_tokens=5))
+    s.run_until_idle()
+    for rid in good:
+        view = s.request(rid)
+        assert view.status is RequestStatus.FINISHED and len(view.output_tokens) == 4, view
+    assert s.request("a").output_tokens == (4, 5, 6, 7)
+    with pytest.raises(KeyError):
+        s.request("bad-id")
+    assert runner.cache.leased_pages() == [0] and s.snapshot().reserved_blocks == (0,)
