@@ -109,6 +109,7 @@ class CacheManager:
         self._run_state: dict[int, object] = {}  # run -> state tensor [max_requests, *shape]
         self._state_specs: dict[int, StateSpec] = {}
         self._requests: dict[object, RequestCache] = {}
+        self.guarded: list = []          # GuardedBuffers behind the groups' storage (CUDA only)
         by_spec: dict[PagedKVSpec, LayerGroup] = {}
         for run, need in enumerate(needs):
             if run in self.shares:
@@ -137,15 +138,25 @@ class CacheManager:
     def _allocate_storage(self) -> None:
         import torch
 
+        self.guarded = []
         for group in self.groups:
             spec = group.spec
             # one page more than the pool leases: ``null_page`` takes the keys of filler
             # entries of fixed-size (graph-replayed) batches and is never read back
-            group.storage = torch.zeros(
-                (len(group.units), 2, self.num_pages + 1, spec.num_kv_heads, self.page_size, spec.head_dim),
-                dtype=self.dtype,
-                device=self.device,
-            )
+            shape = (len(group.units), 2, self.num_pages + 1, spec.num_kv_heads, self.page_size, spec.head_dim)
+            numel = 1
+            for extent in shape:
+                numel *= extent
+            if torch.device(self.device).type == "cuda":
+                # canary words before and after the pool: a write to "page -1" or past the
+                # last page shows in ``native.damaged_canaries(cache.guarded)``
+                from ..ops.native import GuardedBuffer
+
+                buffer = GuardedBuffer(f"cache pool of layer group {group.index}", numel, self.dtype, self.device, zero=True)
+                self.guarded.append(buffer)
+                group.storage = buffer.data.view(shape)
+            else:
+                group.storage = torch.zeros(shape, dtype=self.dtype, device=self.device)
         for run, spec in self._state_specs.items():
             self._run_state[run] = torch.zeros(
                 (self.max_requests + 1, *spec.shape), dtype=getattr(torch, spec.dtype), device=self.device

@@ -956,18 +956,23 @@ bool ensure_encode() {
   return g_encode_tiled != nullptr;
 }
 
-const CUtensorMap* cache_map(const void* base, int rows, int page_size, bool lines = false) {
+// The map is copied into *out: the table below may drop its entries when it grows large,
+// so no caller keeps a pointer into it.
+bool cache_map(CUtensorMap* out, const void* base, int rows, int page_size, bool lines = false) {
   // lines: the matrix seen as [rows * D/64 lines, 64 columns]; a box is a whole page chunk
   // (page_size * D/64 lines, contiguous in memory)
   static std::map<std::tuple<const void*, int, int, bool>, CUtensorMap> maps;
   const auto key = std::make_tuple(base, rows, page_size, lines);
   auto found = maps.find(key);
-  if (found != maps.end()) return &found->second;
-  if (!ensure_encode()) return nullptr;
+  if (found != maps.end()) {
+    *out = found->second;
+    return true;
+  }
+  if (!ensure_encode()) return false;
   EncodeTiledFn encode = g_encode_tiled;
   CUtensorMap map;
   const int per_row = lines ? D / 64 : 1;
-  if (page_size * per_row > 256) return nullptr;
+  if (page_size * per_row > 256) return false;
   cuuint64_t dims[2] = {(cuuint64_t)(lines ? 64 : D), (cuuint64_t)rows * per_row};
   cuuint64_t strides[1] = {(cuuint64_t)(lines ? 64 : D) * 2};
   cuuint32_t box[2] = {64u, (cuuint32_t)(page_size * per_row)};
@@ -975,13 +980,16 @@ const CUtensorMap* cache_map(const void* base, int rows, int page_size, bool lin
   if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return nullptr;
+    return false;
   if (maps.size() > 4096) maps.clear();
-  return &maps.emplace(key, map).first->second;
+  maps.emplace(key, map);
+  *out = map;
+  return true;
 }
 
 }  // namespace
 
+#include "attention_noalloc.h"
 #include "attention_tc5.cuh"
 #include "attention_balanced.cuh"
 
@@ -1054,8 +1062,9 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
       static const bool force_mma = getenv("FORGE_ENGINE_PREFILL_MMA") != nullptr && getenv("FORGE_ENGINE_PREFILL_MMA")[0] == '1';
       const bool tc5_ok = !force_mma && (D == 128 || D == 64) && (TC5_ROWS % groups) == 0 && page_size <= TC5_KEYS &&
                           page_size * 32 >= TC5_KEYS && (TC5_KEYS % page_size) == 0 && scale > 0.f && ensure_encode();
-      const CUtensorMap* mk = tc5_ok ? cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
-      const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size) : nullptr;
+      CUtensorMap mk_copy, mv_copy;
+      const CUtensorMap* mk = tc5_ok && cache_map(&mk_copy, k_cache, num_pages * num_kv_heads * page_size, page_size) ? &mk_copy : nullptr;
+      const CUtensorMap* mv = mk && cache_map(&mv_copy, v_cache, num_pages * num_kv_heads * page_size, page_size) ? &mv_copy : nullptr;
       CUtensorMap mq;
       if (mk && mv && make_query_map(&mq, q, q_stride, total_tokens, num_kv_heads * groups, groups) == 0) {
         static bool tc5_configured = false;
@@ -1082,8 +1091,9 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
     // the step's tiles spread evenly over as many blocks as the GPU holds at once
     if (workspace == nullptr || entries > BAL_MAX_ENTRIES) return FE_ERR_BAD_SHAPE;
     if ((D % 64) != 0 || page_size > BN || (BN % page_size) != 0) return FE_ERR_BAD_SHAPE;
-    const CUtensorMap* mk = cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size, true);
-    const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size, true) : nullptr;
+    CUtensorMap mk_copy, mv_copy;
+    const CUtensorMap* mk = cache_map(&mk_copy, k_cache, num_pages * num_kv_heads * page_size, page_size, true) ? &mk_copy : nullptr;
+    const CUtensorMap* mv = mk && cache_map(&mv_copy, v_cache, num_pages * num_kv_heads * page_size, page_size, true) ? &mv_copy : nullptr;
     if (!mk || !mv) return FE_ERR_BAD_SHAPE;
     const int blocks = SYM(fe_attn_balanced_blocks_d)();
     if (blocks <= 0) return FE_ERR_BAD_SHAPE;
@@ -1103,8 +1113,9 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
     dim3 grid(num_splits, entries, num_kv_heads);
     int rc = 0;
     const bool tma_ok = (D % 64) == 0 && page_size <= BN && (BN % page_size) == 0 && (num_splits == 1 || counters != nullptr);
-    const CUtensorMap* mk = tma_ok ? cache_map(k_cache, num_pages * num_kv_heads * page_size, page_size, true) : nullptr;
-    const CUtensorMap* mv = mk ? cache_map(v_cache, num_pages * num_kv_heads * page_size, page_size, true) : nullptr;
+    CUtensorMap mk_copy, mv_copy;
+    const CUtensorMap* mk = tma_ok && cache_map(&mk_copy, k_cache, num_pages * num_kv_heads * page_size, page_size, true) ? &mk_copy : nullptr;
+    const CUtensorMap* mv = mk && cache_map(&mv_copy, v_cache, num_pages * num_kv_heads * page_size, page_size, true) ? &mv_copy : nullptr;
     if (mk && mv) {
       static bool tma_configured = false;
       if (!tma_configured) {
@@ -1138,11 +1149,11 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
 // ---------------------------------------------------------------------------
 
 // Scratch for the splits' partial results, held by every GPU that loads this library
-// until the process exits: 1,048,576 floats = 4 MiB.
-#define FE_NOALLOC_SCRATCH_FLOATS (1 << 20)
+// until the process exits: 1,048,576 floats = 4 MiB (the size and the error code are the
+// header's, so that declaration and definition cannot drift apart).
+#define FE_NOALLOC_SCRATCH_FLOATS FE_ATTENTION_NOALLOC_SCRATCH_FLOATS
 static __device__ __align__(256) float fe_noalloc_scratch[FE_NOALLOC_SCRATCH_FLOATS];
 
-#define FE_ERR_SCRATCH_TOO_SMALL 10005
 #define FE_NOALLOC_MAX_DEVICES 64
 
 FE_EXPORT int SYM(fe_attention_decode_noalloc_d)(const void* q, int q_stride, void* out,
@@ -1161,7 +1172,8 @@ FE_EXPORT int SYM(fe_attention_decode_noalloc_d)(const void* q, int q_stride, vo
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return FE_ERR_BAD_ALIGN;
   if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
-  const long long needed = (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
+  // with one split a block writes its result straight to `out` and the array is not touched
+  const long long needed = num_splits == 1 ? 0 : (long long)entries * num_kv_heads * num_splits * DEC_ROWS * (D + 2);
   if (needed > FE_NOALLOC_SCRATCH_FLOATS) {
     fprintf(stderr,
             "fe_attention_decode_noalloc: entries=%d x kv_heads=%d x splits=%d needs %lld floats of scratch, "

@@ -15,9 +15,13 @@
  * The caller still passes every input and the output buffer.
  *
  * One function per head size, in the library built for that head size
- * (libforge_engine_b200_attn_d<HEAD>.so, compiled with -DFE_HEAD_DIM=<HEAD>):
+ * (libforge_engine_b200_attn_d<HEAD>.so, compiled with -DFE_HEAD_DIM=<HEAD>; HEAD is any
+ * multiple of 16 from 16 to 256):
  *
  *   int fe_attention_decode_noalloc_d<HEAD>(...same leading arguments as below...);
+ *
+ * The prototypes for 64 and 128 are declared at the end of this file; for another head
+ * size write FE_DECLARE_ATTENTION_DECODE_NOALLOC(<HEAD>); after including it.
  *
  * Arguments
  *   q, q_stride     bfloat16 queries; row n starts at q + n * q_stride elements and holds
@@ -37,8 +41,9 @@
  *   status          int32 device word; bit 2 is set if a needed page is missing
  *   stream          the CUDA stream to launch on
  * Returns 0 on success; 10002 for a shape it does not take; 10003 for misalignment;
- * 10005 when entries * num_kv_heads * num_splits * 16 * (HEAD + 2) exceeds the scratch
- * (1,048,576 floats = 4 MiB; a line naming the sizes is also written to stderr); any
+ * 10005 when num_splits > 1 and entries * num_kv_heads * num_splits * 16 * (HEAD + 2)
+ * exceeds the scratch (1,048,576 floats = 4 MiB; a line naming the sizes is also written to
+ * stderr; with one split the array is not used and any number of entries is taken); any
  * other non-zero value is a cudaError_t.
  *
  * What to know
@@ -47,7 +52,10 @@
  *     until the process exits.
  *   - The first call on each device looks the array's device address up
  *     (cudaGetSymbolAddress) and raises the kernel's shared-memory limit, with that
- *     device current.  Make that first call outside of any stream capture.
+ *     device current.  Make that first call outside of any stream capture, and from one
+ *     host thread: the table of looked-up addresses is a plain static, so two threads
+ *     making a device's first call at the same moment would race on it (later calls only
+ *     read it and may come from any thread).
  *   - All calls on a device share the one array, and it keeps what the last call left.
  *     Nothing in it has to start at zero: every slot a call reads is written earlier in
  *     that same call.  Two calls that overlap on the GPU (different streams, or the same

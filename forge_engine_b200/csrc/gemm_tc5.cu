@@ -21,7 +21,11 @@
 //   adds them.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the block sets a bit in the
-// status word, stops issuing work, frees its tensor memory and returns.
+// status word, stops issuing work, frees its tensor memory and returns.  The bound is far
+// longer than any copy takes, so by the time it is hit the block's own copies in flight have
+// landed.  fe_gemm_tc5_set_test_fault makes one wait run out on purpose (a short bound and a
+// producer that leaves out one load), so that a test can see the status word and that the
+// device is usable afterwards; nothing traps, faults or spins on.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -67,6 +71,8 @@ struct GemmParams {
   float* ws_part;        // [feature tiles, token tiles, ksplit, BN, BM] floats
   unsigned* ws_count;    // [feature tiles * token tiles], zero before and after a launch
   int* status;
+  unsigned wait_limit;   // polls a wait may take before the block gives up
+  int skip_kblock;       // test fault: the producer leaves out the load of this k-block (-1: none)
   QkvRope rope;          // EPI_QKV_ROPE only
 };
 
@@ -89,8 +95,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
   return ok != 0;
 }
 // Bounded wait: false when the limit was hit or another role has already given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag) {
-  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag,
+                                          unsigned limit = WAIT_LIMIT) {
+  for (unsigned i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
@@ -322,16 +329,18 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       // tiles first, then wait for that kernel, then fetch the token tiles.
       const int ahead = min(STAGES, my_blocks);
       for (int i = 0; i < ahead; ++i) {
+        if (kb_begin + i == p.skip_kblock) continue;      // test fault: this stage never fills
         mbar_expect_tx(full + i, A_BYTES + B_BYTES);
         tma_load_2d(a_tiles + i * A_BYTES, &map_w, (kb_begin + i) * BK, m0, full + i);
       }
       pdl_wait();
       for (int i = 0; i < ahead; ++i)
-        tma_load_2d(b_tiles + i * B_BYTES, &map_x, (kb_begin + i) * BK, n0, full + i);
+        if (kb_begin + i != p.skip_kblock) tma_load_2d(b_tiles + i * B_BYTES, &map_x, (kb_begin + i) * BK, n0, full + i);
       for (int i = ahead; i < my_blocks; ++i) {
         const int s = i % STAGES;
         const unsigned parity = ((i / STAGES) & 1) ^ 1;
-        if (!mbar_wait(empty + s, parity, abort_flag)) break;
+        if (!mbar_wait(empty + s, parity, abort_flag, p.wait_limit)) break;
+        if (kb_begin + i == p.skip_kblock) continue;      // test fault: this stage never fills
         mbar_expect_tx(full + s, A_BYTES + B_BYTES);
         const int kcoord = (kb_begin + i) * BK;
         tma_load_2d(a_tiles + s * A_BYTES, &map_w, kcoord, m0, full + s);
@@ -345,7 +354,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       for (int i = 0; i < my_blocks && ok; ++i) {
         const int s = i % STAGES;
         const unsigned parity = (i / STAGES) & 1;
-        ok = mbar_wait(full + s, parity, abort_flag);
+        ok = mbar_wait(full + s, parity, abort_flag, p.wait_limit);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t da = umma_desc(a_tiles + s * A_BYTES);
@@ -363,7 +372,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     // epilogue warps 2..5 own accumulator lanes 32 * (warp % 4) .. +31
     const int quarter = warp & 3;
     const int feature = m0 + quarter * 32 + lane;
-    mbar_wait(acc_done, 0, abort_flag);
+    mbar_wait(acc_done, 0, abort_flag, p.wait_limit);
     pdl_wait();   // returns at once after the producer's wait; orders this warp's own global accesses
     // all four epilogue warps take the same path: agree on the outcome of the wait
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -629,7 +638,20 @@ int launch_bn(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
   return FE_ERR_BAD_DTYPE;
 }
 
+// Test fault (see the head of this file); 0 / -1: none.
+unsigned g_test_wait_limit = 0;
+int g_test_skip_kblock = -1;
+
 }  // namespace
+
+// For tests of the bounded waits only: launches after this call poll at most `wait_limit`
+// times per wait (0: the usual bound) and their producers leave out the load of k-block
+// `skip_kblock` (-1: none), so that the block waiting for it gives up, sets
+// FE_STATUS_WAIT_TIMEOUT and returns.  Call with (0, -1) to go back to normal.
+FE_EXPORT void fe_gemm_tc5_set_test_fault(unsigned wait_limit, int skip_kblock) {
+  g_test_wait_limit = wait_limit;
+  g_test_skip_kblock = skip_kblock;
+}
 
 // Token-tile width the kernel uses for n tokens.
 FE_EXPORT int fe_gemm_tc5_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256))); }
@@ -651,7 +673,8 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
   rc = make_map(&mx, x, n, k, bn);
   if (rc) return rc;
   const int cluster_reduce = (ksplit > 1 && ksplit <= 8 && bn <= CLUSTER_REDUCE_TOKENS) ? 1 : 0;
-  GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, ws_part, ws_count, status, rope ? *rope : QkvRope{}};
+  GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, ws_part, ws_count, status,
+               g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT, g_test_skip_kblock, rope ? *rope : QkvRope{}};
   dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
   if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;
   switch (bn) {

@@ -21,6 +21,7 @@ from ..weights.loader import open_checkpoint
 from ..weights.random_init import RandomTensors
 from .batch import StepBatch, StepEntry, build_batch
 from .graphs import DecodeGraphs
+from .timing import StepTimer
 
 DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16,
           "fp32": torch.float32}
@@ -41,9 +42,15 @@ class ModelRunner:
     """Owns the model, the cache manager and the device status word."""
 
     def __init__(self, model: DecoderModel, *, page_size: int, num_pages: int, max_requests: int,
-                 use_graphs: bool = True) -> None:
+                 use_graphs: bool = True, timing: bool = False) -> None:
+        """With ``timing`` every part's call is bracketed by CUDA events (``timings()``
+        reads them); timed steps are launched kernel by kernel, never replayed from a graph."""
         self.model = model
         self.ctx = model.ctx
+        self.timer = None
+        if timing:
+            self.timer = self.ctx.timer = StepTimer()
+            use_graphs = False
         needs, shares = model.cache_needs()
         self.cache = CacheManager(
             needs,
@@ -62,7 +69,8 @@ class ModelRunner:
     # -- construction ------------------------------------------------------------------
     @classmethod
     def from_folder(cls, folder: str | Path, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
-                    num_pages: int = 1024, max_requests: int = 16, use_graphs: bool = True) -> "ModelRunner":
+                    num_pages: int = 1024, max_requests: int = 16, use_graphs: bool = True,
+                    timing: bool = False) -> "ModelRunner":
         """Model class by config.json's architecture, weights by tensor name."""
         native.require_cuda()
         native.lib()
@@ -75,12 +83,12 @@ class ModelRunner:
         weights = open_checkpoint(folder, expected, engine_dtype, device, optional)
         return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
                                 num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs,
-                                architecture=arch)
+                                architecture=arch, timing=timing)
 
     @classmethod
     def from_random(cls, config: dict, seed: int, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
                     num_pages: int = 1024, max_requests: int = 16, std: float = 0.02,
-                    use_graphs: bool = True) -> "ModelRunner":
+                    use_graphs: bool = True, timing: bool = False) -> "ModelRunner":
         """Random weights drawn on the device (benchmark-sized models never touch the disk)."""
         native.require_cuda()
         native.lib()
@@ -89,11 +97,12 @@ class ModelRunner:
         weights = RandomTensors(arch.expected_tensors(spec), seed, std=std, dtype=engine_dtype, device=device)
         return cls.from_tensors(spec, weights, dtype=engine_dtype, device=device, page_size=page_size,
                                 num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs,
-                                architecture=arch)
+                                architecture=arch, timing=timing)
 
     @classmethod
     def from_tensors(cls, spec, weights: dict, *, dtype, device, page_size: int, num_pages: int,
-                     max_requests: int, use_graphs: bool = True, architecture=None) -> "ModelRunner":
+                     max_requests: int, use_graphs: bool = True, architecture=None,
+                     timing: bool = False) -> "ModelRunner":
         """``architecture`` (a registry entry) assembles the model; None builds the decoder of
         ``models/decoder.py``."""
         native.require_cuda()
@@ -110,7 +119,7 @@ class ModelRunner:
             if hasattr(weights, "close"):
                 weights.close()       # a lazily read checkpoint reports NaN and infinities here
             return cls(model, page_size=page_size, num_pages=num_pages, max_requests=max_requests,
-                       use_graphs=use_graphs)
+                       use_graphs=use_graphs, timing=timing)
 
     # -- requests ------------------------------------------------------------------------
     def begin(self, key) -> None:
@@ -185,9 +194,23 @@ class ModelRunner:
         self.tokens_run += n_tokens
         return logits
 
+    def timings(self, reset: bool = False) -> dict:
+        """Device time per part over the steps run so far (needs ``timing=True``):
+        ``{"steps", "tokens", "parts": {name: {calls, total_ms, minimum, p10, median, p90,
+        maximum}}}``; "mixer" and "ffn" are whole parts, "mixer.*" what the mixer does inside."""
+        if self.timer is None:
+            raise ForgeEngineError("this runner was built without timing=True")
+        out = {"steps": self.steps_run, "tokens": self.tokens_run, "parts": self.timer.collect()}
+        if reset:
+            self.timer.reset()
+        return out
+
     def check_status(self) -> None:
         """Read the device status word (synchronises) and raise if a kernel flagged anything."""
         value = int(self.ctx.status.item())
+        damaged = native.damaged_canaries(self.cache.guarded)
+        if damaged:
+            raise ForgeEngineError("canary words were overwritten beside: " + ", ".join(damaged))
         if value:
             self.ctx.status.zero_()
             reasons = [text for bit, text in native.STATUS_BITS.items() if value & bit]

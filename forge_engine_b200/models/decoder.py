@@ -109,11 +109,14 @@ class DecoderModel:
         n = batch.n_tokens
         batch.shared.clear()      # what parts share lives for one pass only (a batch may be run again)
         h = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.ctx.device)
-        native.embedding(batch.token_ids, self.embed, h, self.ctx.status)
+        with self.ctx.section("embedding"):
+            native.embedding(batch.token_ids, self.embed, h, self.ctx.status)
         pending = None
         for index, run in enumerate(self.spec.schedule):
             pending = self.blocks[run.layer].forward(h, pending, batch, cache.view(index))
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.ctx.device)
-        normed = self.final_norm.add_forward(h, pending, row_map=batch.want_rows)
-        return self.head(normed, out_dtype=torch.float32)
+        with self.ctx.section("final_norm"):
+            normed = self.final_norm.add_forward(h, pending, row_map=batch.want_rows)
+        with self.ctx.section("head"):
+            return self.head(normed, out_dtype=torch.float32)

@@ -110,6 +110,78 @@ def check(code: int, what: str) -> None:
     raise ForgeEngineError(f"{what}: CUDA error {code}")
 
 
+# ---------------------------------------------------------------------------
+# scratch memory with canary words
+# ---------------------------------------------------------------------------
+
+CANARY = 0x5AFEC0DE
+GUARD_BYTES = 256
+
+
+class GuardedBuffer:
+    """A device buffer with ``GUARD_BYTES`` of a fixed bit pattern before and after it.
+
+    Stands in for a memory checker: a kernel that writes one element before or past its
+    scratch (or its cache pool) changes a canary word, which ``damaged()`` reports."""
+
+    def __init__(self, name: str, numel: int, dtype: torch.dtype, device, zero: bool = False) -> None:
+        self.name = name
+        item = torch.empty((), dtype=dtype).element_size()
+        guard = GUARD_BYTES // item
+        body = -(-max(1, numel) // guard) * guard          # the rear guard starts 256-byte aligned
+        flat = (torch.zeros if zero else torch.empty)(guard + body + guard, dtype=dtype, device=device)
+        self._flat = flat
+        self.data = flat[guard : guard + numel]
+        self._guards = (flat[:guard].view(torch.int32), flat[guard + body :].view(torch.int32))
+        for words in self._guards:
+            words.fill_(CANARY)
+
+    def numel(self) -> int:
+        return self.data.numel()
+
+    def damaged(self) -> torch.Tensor:
+        """0-d bool tensor on the device: a canary word was overwritten."""
+        return (self._guards[0] != CANARY).any() | (self._guards[1] != CANARY).any()
+
+
+class _Scratch:
+    """Scratch buffers of this module, per (kind, device).  A buffer that turns out too
+    small is replaced by a larger one; the old one stays referenced, because a captured CUDA
+    graph may still hold its address."""
+
+    def __init__(self) -> None:
+        self.current: dict = {}
+        self.all: list = []
+
+    def get(self, kind: str, device, numel: int, dtype: torch.dtype, floor: int, zero: bool = False) -> torch.Tensor:
+        key = (kind, torch.device(device))
+        buffer = self.current.get(key)
+        if buffer is None or buffer.numel() < numel:
+            buffer = GuardedBuffer(f"{kind} scratch", max(numel, floor), dtype, device, zero)
+            self.current[key] = buffer
+            self.all.append(buffer)
+        return buffer.data
+
+
+_scratch = _Scratch()
+
+
+def damaged_canaries(extra=()) -> list:
+    """Names of the scratch buffers of this module (and of ``extra`` GuardedBuffers, such as
+    the cache pools) whose canary words no longer hold their pattern; synchronises."""
+    buffers = list(_scratch.all) + list(extra)
+    if not buffers:
+        return []
+    by_device: dict = {}
+    for buffer in buffers:
+        by_device.setdefault(buffer.data.device, []).append(buffer)
+    bad = []
+    for group in by_device.values():
+        flags = torch.stack([b.damaged() for b in group]).cpu().tolist()
+        bad.extend(b.name for b, flag in zip(group, flags) if flag)
+    return bad
+
+
 def require_cuda() -> None:
     if not torch.cuda.is_available():
         raise CUDAUnavailableError("no CUDA device: this engine runs on the GPU only")
@@ -300,16 +372,15 @@ def attention_balanced_blocks(head_dim: int) -> int:
     return blocks
 
 
-_attn_counters: dict = {}
-
-
 def _attention_counters(device, pairs: int) -> torch.Tensor:
     """Zeroed arrival counters, one per (entry, kv head); launches leave them zeroed."""
-    counters = _attn_counters.get(device)
-    if counters is None or counters.numel() < pairs:
-        counters = torch.zeros(max(pairs, 8192), dtype=torch.int32, device=device)
-        _attn_counters[device] = counters
-    return counters
+    return _scratch.get("attention counters", device, pairs, torch.int32, 8192, zero=True)
+
+
+def _attention_workspace(device, floats: int) -> torch.Tensor:
+    """Partial results of split decode attention.  One buffer per device serves every layer:
+    a layer's attention has combined its parts before the next layer's begins."""
+    return _scratch.get("attention workspace", device, floats, torch.float32, 1 << 22)
 
 
 ATTN_DECODE_ROWS = 16  # rows (new tokens x heads per kv head) the split decode kernel takes
@@ -349,10 +420,10 @@ def attention_mma(
         blocks = attention_balanced_blocks(head_dim)
         if blocks <= 0:
             raise UnsupportedShapeError(f"attention_mma: no balanced decode kernel for head size {head_dim}")
-        workspace = torch.empty(2 * blocks * ATTN_DECODE_ROWS * (head_dim + 2), dtype=torch.float32, device=q.device)
+        workspace = _attention_workspace(q.device, 2 * blocks * ATTN_DECODE_ROWS * (head_dim + 2))
     elif run_decode and num_splits > 1:
         floats = entries * nkv * num_splits * ATTN_DECODE_ROWS * (head_dim + 2)
-        workspace = torch.empty(floats, dtype=torch.float32, device=q.device)
+        workspace = _attention_workspace(q.device, floats)
         if merge_in_kernel:
             counters = _attention_counters(q.device, entries * nkv)
     check(
@@ -387,7 +458,6 @@ def gemm_simt(
 
 
 TC5_STORE_BF16, TC5_STORE_F32, TC5_ADD_F32, TC5_SILU_MUL = 0, 1, 2, 3
-_tc5_scratch: dict = {}
 
 
 def tc5_tile(n: int) -> int:
@@ -395,14 +465,20 @@ def tc5_tile(n: int) -> int:
 
 
 def _tc5_workspace(device, tiles: int, ksplit: int, tile_n: int):
-    entry = _tc5_scratch.get(device)
-    need_part, need_count = tiles * ksplit * tile_n * 128, tiles
-    if entry is None or entry[0].numel() < need_part or entry[1].numel() < need_count:
-        part = torch.empty(max(need_part, 1 << 22), dtype=torch.float32, device=device)
-        count = torch.zeros(max(need_count, 16384), dtype=torch.int32, device=device)
-        entry = (part, count)
-        _tc5_scratch[device] = entry
-    return entry
+    """(partial tiles, arrival counters) for k-splits that do not add up inside a cluster."""
+    part = _scratch.get("gemm partial tiles", device, tiles * ksplit * tile_n * 128, torch.float32, 1 << 22)
+    count = _scratch.get("gemm tile counters", device, tiles, torch.int32, 16384, zero=True)
+    return part, count
+
+
+def gemm_tc5_set_test_fault(wait_limit: int = 0, skip_kblock: int = -1) -> None:
+    """For tests of the bounded waits: later ``gemm_tc5`` launches poll at most ``wait_limit``
+    times per wait and leave out the load of k-block ``skip_kblock``, so that a block gives
+    up, sets status bit 8 and returns.  ``(0, -1)`` restores the usual behaviour."""
+    fn = lib().fe_gemm_tc5_set_test_fault
+    fn.argtypes = [ctypes.c_uint, c_int]
+    fn.restype = None
+    fn(int(wait_limit), int(skip_kblock))
 
 
 TC5_MAX_ROWS = 64   # up to this many rows the tcgen05 kernel is used instead of the library GEMM

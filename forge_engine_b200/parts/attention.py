@@ -188,6 +188,26 @@ class GQAttention(Mixer):
         return self._slots
 
     def forward(self, x, batch, cache: CacheView):
+        with self.ctx.section("mixer.qkv_rope_cache"):
+            qkv = self._project(x, batch, cache)
+        k_cache, v_cache = cache.kv
+        table = batch.group_tables[cache.group]
+        out = torch.empty((x.shape[0], self.nq * self.d), dtype=qkv.dtype, device=x.device)
+        groups = self.nq // self.nkv
+        with self.ctx.section("mixer.attention"):
+            if qkv.dtype == torch.bfloat16 and groups <= native.ATTN_DECODE_ROWS:
+                self._tensor_core_attention(qkv, k_cache, v_cache, table, batch, out, groups)
+            else:
+                native.attention_simt(
+                    qkv, qkv.shape[1], k_cache, v_cache, table, batch.positions, batch.token_entry,
+                    self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
+                )
+        with self.ctx.section("mixer.o_proj"):
+            return self.o_proj(out)
+
+    def _project(self, x, batch, cache: CacheView):
+        """q, k, v of the step's tokens: projected, normalised per head, rotated; k and v
+        stored in their pages.  Returns qkv with the finished queries."""
         k_cache, v_cache = cache.kv
         table = batch.group_tables[cache.group]
         rotary = self.position.rotary()
@@ -216,16 +236,7 @@ class GQAttention(Mixer):
                 batch.positions, batch.token_entry, k_cache, v_cache, table, self.nq,
                 cache.owns, self.ctx.status, table=angles,
             )
-        out = torch.empty((x.shape[0], self.nq * self.d), dtype=qkv.dtype, device=x.device)
-        groups = self.nq // self.nkv
-        if qkv.dtype == torch.bfloat16 and groups <= native.ATTN_DECODE_ROWS:
-            self._tensor_core_attention(qkv, k_cache, v_cache, table, batch, out, groups)
-        else:
-            native.attention_simt(
-                qkv, qkv.shape[1], k_cache, v_cache, table, batch.positions, batch.token_entry,
-                self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
-            )
-        return self.o_proj(out)
+        return qkv
 
     def _fused_projection(self, x, rotary, k_cache) -> bool:
         """Whether the q/k/v projection's epilogue can do the per-head norms, the rotation

@@ -22,6 +22,17 @@ from ..cache.manager import CacheNeeds
 from ..errors import ConfigError
 
 
+class _Nothing:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NOTHING = _Nothing()
+
+
 @dataclass
 class BuildContext:
     """What every part may know about its surroundings."""
@@ -29,6 +40,11 @@ class BuildContext:
     dtype: object  # torch.float32 or torch.bfloat16: dtype of activations and of the KV cache
     device: object
     status: object  # int32[1] device word kernels set error bits in
+    timer: object = None  # None, or an object whose ``section(name)`` brackets a part's call with events
+
+    def section(self, name: str):
+        """A context manager round one part's work: records events when a timer is set."""
+        return _NOTHING if self.timer is None else self.timer.section(name)
 
 
 @dataclass(frozen=True)

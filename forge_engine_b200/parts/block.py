@@ -16,6 +16,7 @@ class PreNormBlock:
 
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         """``weights[role]`` is the dict of that part's local tensors."""
+        self.ctx = ctx
         self.input_norm = build_part(spec.input_norm, weights["input_norm"], ctx)
         self.mixer = build_part(spec.mixer, weights["mixer"], ctx)
         self.post_norm = build_part(spec.post_norm, weights["post_norm"], ctx)
@@ -37,10 +38,19 @@ class PreNormBlock:
     def forward(self, h, pending, batch, cache: CacheView):
         """``h`` 32-bit [N, hidden] (in place); ``pending`` the previous block's update or
         None.  Returns this block's feed-forward update, still to be added."""
-        normed = self.input_norm.add_forward(h, pending)
-        update = self.mixer.forward(normed, batch, cache)
-        normed = self.post_norm.add_forward(h, update)
-        return self.ffn.forward(normed)
+        if self.ctx.timer is None:
+            normed = self.input_norm.add_forward(h, pending)
+            update = self.mixer.forward(normed, batch, cache)
+            normed = self.post_norm.add_forward(h, update)
+            return self.ffn.forward(normed)
+        with self.ctx.section("input_norm"):
+            normed = self.input_norm.add_forward(h, pending)
+        with self.ctx.section("mixer"):
+            update = self.mixer.forward(normed, batch, cache)
+        with self.ctx.section("post_norm"):
+            normed = self.post_norm.add_forward(h, update)
+        with self.ctx.section("ffn"):
+            return self.ffn.forward(normed)
 
 
 register_arrangement("pre_norm", PreNormBlock, replace=True)

@@ -7,7 +7,7 @@ Usage (once; the outputs are committed beside this script):
 It imports ``forge_engine.qwen3`` from the given source tree of
 marcoharuni/forge-engine (the package is not installed, so the version lookup in its
 ``__init__`` is answered by a shim), builds ``Qwen3ForCausalLM`` for the tiny
-configurations A and B of ``tests/plain_qwen3.py``, loads the seeded weights of
+configurations A, B and C (C has biases on q/k/v/o) of ``tests/plain_qwen3.py``, loads the seeded weights of
 ``plain_qwen3.seeded_weights`` into it by name and stores, per configuration,
 
 * ``ids``            the token ids that were fed,
@@ -110,6 +110,7 @@ def main() -> None:
     for name, raw, seed, ids_seed in (
         ("tiny_a", plain.TINY_A, 0, 1),
         ("tiny_b", plain.TINY_B, 2, 3),
+        ("tiny_c", plain.TINY_C, 5, 7),
     ):
         tensors = run(qwen3, raw, seed, ids_seed, 24)
         save_file(tensors, str(HERE / f"{name}.safetensors"))

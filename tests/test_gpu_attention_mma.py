@@ -6,7 +6,7 @@ from __future__ import annotations
 import pytest
 import torch
 
-from test_gpu_kernels import DEV, dense_attention, paged_layout, status_word
+from test_gpu_kernels import DEV, dense_attention, paged_layout, plant_keys, status_word
 
 pytestmark = pytest.mark.gpu
 
@@ -20,8 +20,11 @@ def native():
     return module
 
 
-def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, sharp=False, merge_in_kernel=True):
-    """Request r holds lengths[r] keys after the step, the last new_counts[r] of them new."""
+def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, sharp=False, merge_in_kernel=True,
+             plant=True):
+    """Request r holds lengths[r] keys after the step, the last new_counts[r] of them new.
+    ``plant``: the last query of every entry that takes the decode kernel is aimed at single
+    keys on the edges of its window and of its tiles (see ``plant_keys``)."""
     dtype = torch.bfloat16
     k_cache, v_cache, table, keys, values = paged_layout(lengths, page, nkv, d, dtype, seed=d + nq + page)
     g = torch.Generator().manual_seed(2)
@@ -36,6 +39,10 @@ def run_case(native, nq, nkv, d, page, window, lengths, new_counts, splits, shar
         qkv[0, :d] = (keys[0][3, 0].float() * 4).to(dtype)
     groups = nq // nkv
     rows = [c * groups for c in new_counts]
+    if plant:
+        for r, (n, c) in enumerate(zip(lengths, new_counts)):
+            if c * groups <= 16 and n >= 2:
+                plant_keys(k_cache, v_cache, table, keys, values, r, window, qkv[cu[r + 1] - 1, : nq * d])
     out = torch.full((total, nq * d), float("nan"), dtype=dtype, device=DEV)
     status = status_word()
     native.attention_mma(
@@ -84,11 +91,12 @@ def test_prefill_portion_deep_in_a_long_context(native) -> None:
     run_case(native, 8, 2, 128, 16, 1500, [6000, 3000], [1000, 3000], splits=1)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+@pytest.mark.parametrize("splits", [1, 2, 5, 8, 16, 32])
 def test_split_decode_long_contexts(native, splits) -> None:
     lengths = [2048, 1, 777, 64, 65, 4000]
     run_case(native, 32, 8, 128, 16, None, lengths, [1] * 6, splits)
     run_case(native, 32, 8, 128, 16, 500, lengths, [1] * 6, splits)
+    run_case(native, 32, 8, 128, 16, 70, lengths, [1] * 6, splits)
     # the splits combined by a second kernel instead of by the block that arrives last
     run_case(native, 32, 8, 128, 16, None, lengths, [1] * 6, splits, merge_in_kernel=False)
 

@@ -153,6 +153,39 @@ def paged_layout(lengths, page_size, nkv, d, dtype, seed, spare_pages=5):
     return k_cache.to(DEV), v_cache.to(DEV), table.to(DEV), keys, values
 
 
+def plant_keys(k_cache, v_cache, table, keys, values, r, window, q_row):
+    """Make request ``r``'s last query depend on single keys at the places where a kernel
+    can go wrong: the oldest key it may see (the first of its window, or key 0), the key
+    just before it (which a window must hide: it gets the largest score of all and a huge
+    value), both sides of the edges of the first and the last 64-key tile, the middle, and
+    its own key.  ``q_row`` ([nq * d] or longer, the query heads first) is overwritten with
+    the direction all planted keys share, so each of them outweighs all random keys
+    together and a missed, doubled or wrongly admitted key moves the result by far more
+    than the tolerance.  Changes ``keys[r]``, ``values[r]`` and the cache pages alike."""
+    n, nkv, d = keys[r].shape
+    page = k_cache.shape[2]
+    lo = max(0, n - window) if window else 0
+    u = torch.ones(d)
+    u[1::2] = -1.0
+    places = {lo, n - 1, (lo + n) // 2}
+    for edge in (lo + 63, lo + 64, n - 65, n - 64):
+        if lo <= edge < n:
+            places.add(edge)
+    planted = [(pos, 2.0, None) for pos in sorted(places)]
+    if lo > 0:
+        planted.append((lo - 1, 3.0, 50.0))
+    for pos, gain, value in planted:
+        keys[r][pos] = (gain * u).to(keys[r].dtype)
+        if value is not None:
+            values[r][pos] = value
+        at = int(table[r, pos // page])
+        k_cache[at, :, pos % page] = keys[r][pos].to(k_cache.device)
+        v_cache[at, :, pos % page] = values[r][pos].to(v_cache.device)
+    heads = q_row.numel() // d
+    q_row.view(heads, d)[:] = (1.5 * u).to(q_row.dtype)
+    return len(planted)
+
+
 def dense_attention(q, k, v, positions, scale, window):
     """q [T, nq, d] at ``positions``; k, v [S, nkv, d]; 64-bit softmax attention."""
     nq, nkv = q.shape[1], k.shape[1]

@@ -7,6 +7,8 @@ small that pages are used again).  Everything goes through ``bin/trace_run``.
 
 from __future__ import annotations
 
+import json
+
 import numpy as np
 import pytest
 import torch
@@ -61,8 +63,18 @@ def test_replay_modes_match_plain(name: str, dtype: str, tmp_path) -> None:
     trace_modes.mixed(trace, sequences)
     # the pool holds just what the trace's live requests need, so pages are leased again
     got = run_trace(tmp_path / "model", tmp_path / "out", dtype, trace.peak_tokens, trace.steps,
-                    ("--page-size", str(page)))
+                    ("--page-size", str(page), "--page-log", str(tmp_path / "pages.json")))
     assert len(trace.rows) > 300
+    # ... and they were: some physical page was held by different requests at different times,
+    # in every layer group (a windowed group gives pages back while its request lives)
+    held = json.loads((tmp_path / "pages.json").read_text())
+    assert len(held) == len(trace.steps and {e["id"] for s in trace.steps for e in s["entries"]})
+    for group in range(len(held[0]["pages"])):
+        owners: dict = {}
+        for record in held:
+            for page_id in record["pages"][group]:
+                owners.setdefault(page_id, set()).add(record["id"])
+        assert max(len(ids) for ids in owners.values()) >= 2, "no page was leased a second time"
     worst, worst_at = 0.0, None
     for step, row, key, position in trace.rows:
         mine, ref = got[step][row], expected[key][position]

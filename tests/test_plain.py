@@ -14,7 +14,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
 @pytest.mark.parametrize(
-    "name,raw,seed", [("tiny_a", plain.TINY_A, 0), ("tiny_b", plain.TINY_B, 2)]
+    "name,raw,seed", [("tiny_a", plain.TINY_A, 0), ("tiny_b", plain.TINY_B, 2), ("tiny_c", plain.TINY_C, 5)]
 )
 def test_plain_matches_upstream_outputs(name: str, raw: dict, seed: int) -> None:
     golden = load_file(str(GOLDEN / f"{name}.safetensors"))
