@@ -93,7 +93,11 @@ class Engine:
         return self.scheduler.step()
 
     def run_until_idle(self) -> list:
-        return self.scheduler.run_until_idle()
+        """Step until every request has ended; then read the device status word, so that
+        what a kernel flagged (a bad page, a wait that ran out, NaN logits) is raised here."""
+        events = self.scheduler.run_until_idle()
+        self.runner.check_status()
+        return events
 
     def cancel(self, request_id: str) -> bool:
         return self.scheduler.cancel(request_id)
@@ -145,6 +149,7 @@ class Engine:
             view = self.scheduler.request(rid)
             if view.status is RequestStatus.FAILED:
                 raise RuntimeError(f"request {rid} failed: {view.error}")
+            self.runner.check_status()
         finally:
             self.scheduler.cancel(rid)
             self.scheduler.forget(rid)

@@ -206,7 +206,9 @@ class ModelRunner:
         return out
 
     def check_status(self) -> None:
-        """Read the device status word (synchronises) and raise if a kernel flagged anything."""
+        """Read the device status word and the canary words round the cache pools and the
+        scratch buffers (synchronises); raise if a kernel flagged anything or wrote beside
+        its memory."""
         value = int(self.ctx.status.item())
         damaged = native.damaged_canaries(self.cache.guarded)
         if damaged:

@@ -14,6 +14,13 @@ Two precisions:
 * ``dtype=torch.bfloat16`` - the upstream bfloat16 data flow: activations and
   weights in bfloat16, with the variance of the norms, the rotation angles and the
   softmax in 32-bit exactly where the upstream code has them.
+
+Everything runs where the weights live: on the CPU for the tiny configurations, and - for
+the checks at the benchmark's layer sizes, which would take minutes on the CPU - on the
+GPU with plain torch operators (32-bit matrix products without any reduced-precision
+mode; the caller switches TF32 off).  ``weights`` may be any mapping from tensor name to
+tensor, also one that makes a tensor when it is asked for; only one layer's tensors are
+held at a time.
 """
 
 from __future__ import annotations
@@ -97,7 +104,7 @@ def rotary_tables(
     """src/forge_engine/qwen3.py:345-363 - angles in 32-bit, rounded to ``dtype``."""
     frequencies = 1.0 / (
         theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim)
-    )
+    ).to(positions.device)
     phases = positions.float().unsqueeze(-1) * frequencies
     embeddings = torch.cat((phases, phases), dim=-1)
     return embeddings.cos().to(dtype), embeddings.sin().to(dtype)
@@ -114,14 +121,14 @@ def apply_rotary(x: Tensor, cosine: Tensor, sine: Tensor) -> Tensor:
     return x * cosine.unsqueeze(0) + rotate_half(x) * sine.unsqueeze(0)
 
 
-def causal_mask(length: int, dtype: torch.dtype, window: int | None = None) -> Tensor:
+def causal_mask(length: int, dtype: torch.dtype, window: int | None = None, device=None) -> Tensor:
     """src/forge_engine/qwen3.py:384-406 with no past: key j is seen by query i iff j <= i
     (and, with a window, i - j < window)."""
-    positions = torch.arange(length)
+    positions = torch.arange(length, device=device)
     allowed = positions.unsqueeze(0) <= positions.unsqueeze(1)
     if window is not None:
         allowed = allowed & (positions.unsqueeze(1) - positions.unsqueeze(0) < window)
-    mask = torch.zeros((length, length), dtype=dtype)
+    mask = torch.zeros((length, length), dtype=dtype, device=device)
     return mask.masked_fill(~allowed, torch.finfo(dtype).min)
 
 
@@ -152,13 +159,13 @@ def attention(
     q = rms_norm(q, weights[f"{prefix}.q_norm.weight"], cfg.rms_norm_eps).transpose(0, 1)
     k = rms_norm(k, weights[f"{prefix}.k_norm.weight"], cfg.rms_norm_eps).transpose(0, 1)
     v = v.transpose(0, 1)
-    cosine, sine = rotary_tables(torch.arange(length), d, cfg.rope_theta, x.dtype)
+    cosine, sine = rotary_tables(torch.arange(length, device=x.device), d, cfg.rope_theta, x.dtype)
     q = apply_rotary(q, cosine, sine)
     k = apply_rotary(k, cosine, sine)
     k = k.repeat_interleave(groups, dim=0)
     v = v.repeat_interleave(groups, dim=0)
     scores = torch.matmul(q, k.transpose(1, 2)) * d**-0.5
-    scores = scores + causal_mask(length, scores.dtype, window)
+    scores = scores + causal_mask(length, scores.dtype, window, x.device)
     probabilities = torch.softmax(scores, dim=-1, dtype=torch.float32).to(q.dtype)
     out = torch.matmul(probabilities, v).transpose(0, 1).reshape(length, nq * d)
     return linear(out, weights[f"{prefix}.o_proj.weight"], bias("o_proj"))
@@ -187,12 +194,24 @@ def decoder_layer(
     return h + feed_forward(normed, weights, f"{prefix}.mlp")
 
 
+class _Cast:
+    """``weights`` with every tensor converted to ``dtype`` when it is looked up."""
+
+    def __init__(self, weights, dtype: torch.dtype) -> None:
+        self.weights, self.dtype = weights, dtype
+
+    def __getitem__(self, name: str) -> Tensor:
+        return self.weights[name].to(self.dtype)
+
+
 def hidden_states(
     ids: Tensor, weights: dict[str, Tensor], cfg: PlainConfig, dtype: torch.dtype
 ) -> tuple[Tensor, list[Tensor]]:
     """Embedding, all layers, final norm (src/forge_engine/qwen3.py:325-335)."""
-    w = {name: tensor.to(dtype) for name, tensor in weights.items()}
-    h = w["model.embed_tokens.weight"][ids.long()]
+    w = _Cast(weights, dtype)
+    table = w["model.embed_tokens.weight"]
+    h = table[ids.long().to(table.device)]
+    del table
     per_layer = []
     for index in range(cfg.num_hidden_layers):
         h = decoder_layer(h, w, index, cfg)

@@ -694,6 +694,205 @@ def test_toy_routed_feed_forward_and_position_encoding(fe, tmp_path) -> None:
     runner.cache.check_consistency()
 
 
+# ---------------------------------------------------------------------------
+# a third toy: a model assembled by its architecture (scaled embedding), an arrangement
+# that runs mixer and feed-forward side by side (no attribute named "mixer"), and a mixer
+# with state of its own whose decode steps are replayed from CUDA graphs beside filler entries
+# ---------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class ToyRunningSpec:
+    hidden_size: int
+    decay: float
+    kind: str = "toy_running_mixer"
+
+
+def register_toy_parallel():
+    from forge_engine_b200.cache import CacheNeeds, StateSpec
+    from forge_engine_b200.config import (Architecture, AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec,
+                                          NoPositionSpec, NormSpec, RunSpec, register_architecture)
+    from forge_engine_b200.models import DecoderModel
+    from forge_engine_b200.ops import native
+    from forge_engine_b200.parts import Mixer, WeightInfo, build_part, part_class, register_arrangement, register_part
+
+    class ToyRunningMixer(Mixer):
+        """s_t = decay * s_{t-1} + x_t W^T ; y_t = s_t, the state s per request.  A step of
+        single tokens touches the state only through the device tensor ``batch.slots``, so it
+        can be captured and replayed; filler entries of a replayed batch carry the null slot."""
+
+        graph_safe = True
+
+        def __init__(self, spec, weights, ctx):
+            self.spec, self.w, self.dtype = spec, weights["w.weight"].float(), ctx.dtype
+
+        @classmethod
+        def weight_shapes(cls, spec):
+            return {"w.weight": WeightInfo((spec.hidden_size, spec.hidden_size))}
+
+        def cache_needs(self):
+            return CacheNeeds(state=StateSpec((self.spec.hidden_size,), "float32"))
+
+        def forward(self, x, batch, cache):
+            u = x.float() @ self.w.t()
+            if batch.max_new == 1:
+                slots = batch.slots.long()
+                s = self.spec.decay * cache.state.index_select(0, slots) + u
+                cache.state.index_copy_(0, slots, s)
+                return s.to(self.dtype)
+            out = torch.empty_like(u)
+            row = 0
+            for slot, _, count in batch.entries:
+                s = cache.state[slot]
+                for i in range(row, row + count):
+                    s = self.spec.decay * s + u[i]
+                    out[i] = s
+                cache.state[slot] = s
+                row += count
+            return out.to(self.dtype)
+
+    class ParallelBlock:
+        """h += token_mixer(norm(h)) + ffn(norm(h)): one norm, both parts read its output."""
+
+        roles = ("input_norm", "mixer", "ffn")
+
+        def __init__(self, spec, weights, ctx):
+            self.norm = build_part(spec.input_norm, weights["input_norm"], ctx)
+            self.token_mixer = build_part(spec.mixer, weights["mixer"], ctx)
+            self.ffn = build_part(spec.ffn, weights["ffn"], ctx)
+
+        @classmethod
+        def weight_shapes(cls, spec):
+            return {role: part_class(getattr(spec, role)).weight_shapes(getattr(spec, role)) for role in cls.roles}
+
+        def cache_needs(self):
+            return self.token_mixer.cache_needs()
+
+        @property
+        def graph_safe(self):
+            return self.norm.graph_safe and self.token_mixer.graph_safe and self.ffn.graph_safe
+
+        def forward(self, h, pending, batch, cache):
+            normed = self.norm.add_forward(h, pending)
+            return self.token_mixer.forward(normed, batch, cache) + self.ffn.forward(normed)
+
+    class ScaledEmbeddingModel(DecoderModel):
+        """The decoder with its embedding multiplied by a constant of the configuration."""
+
+        def __init__(self, spec, weights, ctx, multiplier):
+            super().__init__(spec, weights, ctx)
+            self.multiplier = multiplier
+
+        def forward(self, batch, cache):
+            batch.shared.clear()
+            h = torch.empty((batch.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=self.ctx.device)
+            native.embedding(batch.token_ids, self.embed, h, self.ctx.status)
+            h.mul_(self.multiplier)
+            pending = None
+            for index, run in enumerate(self.spec.schedule):
+                pending = self.blocks[run.layer].forward(h, pending, batch, cache.view(index))
+            normed = self.final_norm.add_forward(h, pending, row_map=batch.want_rows)
+            return self.head(normed, out_dtype=torch.float32)
+
+    register_part("toy_running_mixer", ToyRunningMixer, replace=True)
+    register_arrangement("toy_parallel", ParallelBlock, replace=True)
+    multipliers = {}
+
+    def spec_of(raw: dict) -> ModelSpec:
+        h = raw["hidden_size"]
+        norm = NormSpec(h, raw["eps"])
+        ffn = GatedMLPSpec(h, raw["inter"])
+        layers = [LayerSpec(norm, ToyRunningSpec(h, raw["decay"]), None, ffn,
+                            {"input_norm": "l0.n", "mixer": "l0.mix", "ffn": "l0.ffn"}, "toy_parallel")]
+        if raw["attention"]:
+            attn = AttentionSpec(h, 4, 2, 16, False, raw["eps"], False, 0.3, NoPositionSpec(), None)
+            layers.append(LayerSpec(norm, attn, norm, ffn,
+                                    {"input_norm": "l1.n1", "mixer": "l1.mix", "post_norm": "l1.n2", "ffn": "l1.ffn"}))
+        schedule = tuple(RunSpec(i) for i in range(len(layers))) + (RunSpec(0),)     # the stateful layer runs twice
+        spec = ModelSpec(raw["vocab"], h, tuple(layers), schedule, norm, True, 4096, (), "emb.weight", "fnorm", "head.weight")
+        multipliers[id(spec)] = raw["embedding_multiplier"]
+        return spec
+
+    def assemble(spec, weights, ctx):
+        return ScaledEmbeddingModel(spec, weights, ctx, multipliers[id(spec)])
+
+    register_architecture(Architecture("ToyParallelForCausalLM", lambda raw: raw, spec_of, assemble=assemble), replace=True)
+
+
+def toy_parallel_plain(ids, w, raw):
+    h = w["emb.weight"][torch.tensor(ids)] * raw["embedding_multiplier"]
+    n, eps = len(ids), raw["eps"]
+
+    def norm(x, name):
+        return plain.rms_norm(x, w[name + ".weight"], eps)
+
+    def running(x, p):
+        u = x @ w[p + ".w.weight"].t()
+        out, s = [], torch.zeros(x.shape[1])
+        for i in range(n):
+            s = raw["decay"] * s + u[i]
+            out.append(s)
+        return torch.stack(out)
+
+    def parallel(h):
+        x = norm(h, "l0.n")
+        return h + running(x, "l0.mix") + plain.feed_forward(x, w, "l0.ffn")
+
+    h = parallel(h)
+    if raw["attention"]:
+        x = norm(h, "l1.n1")
+        q = (x @ w["l1.mix.q_proj.weight"].t()).view(n, 4, 16)
+        k = (x @ w["l1.mix.k_proj.weight"].t()).view(n, 2, 16).repeat_interleave(2, 1)
+        v = (x @ w["l1.mix.v_proj.weight"].t()).view(n, 2, 16).repeat_interleave(2, 1)
+        s = torch.einsum("thd,shd->hts", q, k) * 0.3 + plain.causal_mask(n, q.dtype)
+        h = h + torch.einsum("hts,shd->thd", torch.softmax(s, -1), v).reshape(n, 64) @ w["l1.mix.o_proj.weight"].t()
+        h = h + plain.feed_forward(norm(h, "l1.n2"), w, "l1.ffn")
+    h = parallel(h)          # the same layer again, with a state of its own for this run
+    return norm(h, "fnorm") @ w["emb.weight"].t()
+
+
+@pytest.mark.parametrize("attention", [True, False])
+def test_toy_stateful_mixer_replayed_from_graphs_beside_fillers(fe, tmp_path, attention) -> None:
+    """Registered from this file alone.  Three requests decode together: the batch is padded
+    to four entries and replayed from a CUDA graph; the filler's state goes to the null slot,
+    not to the slot of a live request.  Without the attention layer the model keeps no pages
+    at all, only state."""
+    from forge_engine_b200.config import read_model_config
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+    from forge_engine_b200.weights import random_tensors, write_model_folder
+
+    register_toy_parallel()
+    raw = {"architectures": ["ToyParallelForCausalLM"], "hidden_size": 64, "inter": 80, "vocab": 89, "eps": 1e-5,
+           "decay": 0.7, "embedding_multiplier": 3.0, "attention": attention}
+    arch, _, spec = read_model_config(raw)
+    tensors = random_tensors(arch.expected_tensors(spec), seed=4, std=0.1)
+    write_model_folder(tmp_path / "toy3", raw, tensors)
+    runner = ModelRunner.from_folder(tmp_path / "toy3", dtype="float32", page_size=4, num_pages=64, max_requests=3)
+    assert type(runner.model).__name__ == "ScaledEmbeddingModel" and runner.use_graphs
+    assert len(runner.cache.groups) == (1 if attention else 0)
+    assert runner.cache.state_of_run(0).shape == (4, 64)            # three requests and the null slot
+    w = {k: v.float() for k, v in tensors.items()}
+    ids = {k: random_ids(89, n, 40 + n) for k, n in (("a", 30), ("b", 17), ("c", 22))}
+    refs = {k: toy_parallel_plain(v, w, raw) for k, v in ids.items()}
+    fed = {"a": 9, "b": 2, "c": 6}
+    for k in ids:                                                    # a holds slot 0, the slot a filler must not touch
+        runner.begin(k)
+        out = runner.step([StepEntry(k, ids[k][: fed[k]], range(fed[k]))]).cpu()
+        torch.testing.assert_close(out, refs[k][: fed[k]], atol=5e-5, rtol=1e-4)
+    assert runner.cache.request("a").slot == 0
+    live = ["a", "b", "c"]
+    while live:
+        out = runner.step([StepEntry(k, [ids[k][fed[k]]], [0]) for k in live]).cpu()
+        for row, k in enumerate(live):
+            torch.testing.assert_close(out[row], refs[k][fed[k]], atol=5e-5, rtol=1e-4)
+            fed[k] += 1
+        for k in [k for k in live if fed[k] == len(ids[k])]:
+            runner.end(k)
+            live.remove(k)
+    runner.check_status()
+    assert {key[0] for key in runner.graphs.captured} == {4, 2, 1}   # 3 live (one filler), then 2, then 1
+    runner.cache.check_consistency()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graph_replay_equals_eager_steps(fe, dtype, tmp_path) -> None:
     """Decode steps replayed from CUDA graphs (padded to bucket sizes, fixed table widths)
