@@ -9,6 +9,8 @@ cache, is all data of the spec; this class has no sizes of its own.
 
 from __future__ import annotations
 
+from collections.abc import Mapping
+
 import torch
 
 from ..config.specs import ModelSpec
@@ -36,6 +38,26 @@ def expected_tensors(spec: ModelSpec) -> dict:
     return out
 
 
+class _Scoped(Mapping):
+    """The tensors of one part by their local names: ``view[local]`` looks
+    ``weights[prefix.local]`` up at that moment (a checkpoint that reads on access puts the
+    tensor on the device then), so a part holds only what it keeps."""
+
+    def __init__(self, weights, prefix: str, names) -> None:
+        self._weights, self._prefix, self._names = weights, prefix, tuple(names)
+
+    def __getitem__(self, local: str):
+        if local not in self._names:
+            raise KeyError(local)
+        return self._weights[f"{self._prefix}.{local}"]
+
+    def __iter__(self):
+        return iter(self._names)
+
+    def __len__(self) -> int:
+        return len(self._names)
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, weights: dict, ctx: BuildContext) -> None:
         self.spec = spec
@@ -47,14 +69,10 @@ class DecoderModel:
             per_role = {}
             for role, shapes in block_cls.weight_shapes(layer).items():
                 prefix = layer.names[role]
-                per_role[role] = {local: weights[f"{prefix}.{local}"] for local in shapes}
+                per_role[role] = _Scoped(weights, prefix, shapes)
             self.blocks.append(block_cls(layer, per_role, ctx))
         norm_shapes = part_class(spec.final_norm).weight_shapes(spec.final_norm)
-        self.final_norm = build_part(
-            spec.final_norm,
-            {local: weights[f"{spec.final_norm_name}.{local}"] for local in norm_shapes},
-            ctx,
-        )
+        self.final_norm = build_part(spec.final_norm, _Scoped(weights, spec.final_norm_name, norm_shapes), ctx)
         self.head = Linear(self.embed if spec.tie_embeddings else weights[spec.head_name], status=ctx.status)
         for index, run in enumerate(spec.schedule):
             if not 0 <= run.layer < len(self.blocks):

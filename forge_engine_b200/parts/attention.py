@@ -18,7 +18,7 @@ from ..cache.manager import CacheNeeds, PagedKVSpec
 from ..errors import UnsupportedShapeError
 from ..ops import native
 from .base import BuildContext, CacheView, Mixer, WeightInfo, build_part, register_part
-from .linear import Linear, fuse_rows
+from .linear import Linear, fused_rows
 
 
 # Blocks of a decode kernel the GPU holds at once when nothing says otherwise (two per SM on
@@ -137,14 +137,16 @@ class GQAttention(Mixer):
         self.ctx = ctx
         self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
         bias = None
+        rows = [self.nq * self.d, self.nkv * self.d, self.nkv * self.d]
         if spec.bias:
-            bias = fuse_rows([weights["q_proj.bias"], weights["k_proj.bias"], weights["v_proj.bias"]])
+            bias = fused_rows(weights, ["q_proj.bias", "k_proj.bias", "v_proj.bias"], rows)
+        # q, k and v are looked up one at a time and copied into the fused tensor
         self.qkv_proj = Linear(
-            fuse_rows([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]]),
+            fused_rows(weights, ["q_proj.weight", "k_proj.weight", "v_proj.weight"], rows),
             bias,
             status=ctx.status,
         )
-        self.o_proj = Linear(weights["o_proj.weight"], weights.get("o_proj.bias") if spec.bias else None,
+        self.o_proj = Linear(weights["o_proj.weight"], weights["o_proj.bias"] if spec.bias else None,
                              status=ctx.status)
         self.q_norm = self.k_norm = None
         if spec.qk_norm:

@@ -8,7 +8,7 @@ import torch
 from ..errors import ConfigError
 from ..ops import native
 from .base import BuildContext, FeedForward, WeightInfo, register_part
-from .linear import Linear, fuse_rows, interleave_rows
+from .linear import Linear, fused_rows, interleaved_rows
 
 GATE_UP_BLOCK = 16
 
@@ -23,8 +23,11 @@ class GatedMLP(FeedForward):
         # Rows of the fused weight alternate 16 gate and 16 up features where the size allows:
         # the tensor-core kernel then finishes silu(gate) * up in its epilogue.
         self.block = GATE_UP_BLOCK if self.inter % GATE_UP_BLOCK == 0 else 0
-        gate, up = weights["gate_proj.weight"], weights["up_proj.weight"]
-        fused = interleave_rows(gate, up, self.block) if self.block else fuse_rows([gate, up])
+        # the sources are looked up one at a time and copied into the fused tensor
+        if self.block:
+            fused = interleaved_rows(weights, "gate_proj.weight", "up_proj.weight", self.inter, self.block)
+        else:
+            fused = fused_rows(weights, ["gate_proj.weight", "up_proj.weight"], [self.inter, self.inter])
         self.gate_up = Linear(fused, status=ctx.status)
         self.down = Linear(weights["down_proj.weight"], status=ctx.status)
 

@@ -77,6 +77,42 @@ class Linear:
         return out
 
 
+def fused_rows(weights, names: list, rows: list) -> torch.Tensor:
+    """``weights[name]`` for the names in order, stacked along rows (``rows[i]`` of them
+    each) into one tensor that is allocated first.  Each source is looked up when its turn
+    comes and dropped once copied: with a mapping that reads tensors on access, only one
+    source exists beside the result at any time.  Sources stored in different dtypes make
+    the result 32-bit (exact for bfloat16)."""
+    out, at = None, 0
+    for name, count in zip(names, rows):
+        tensor = weights[name]
+        if tensor.shape[0] != count:
+            raise ValueError(f"{name}: {tensor.shape[0]} rows, {count} expected")
+        if out is None:
+            out = torch.empty((sum(rows), *tensor.shape[1:]), dtype=tensor.dtype, device=tensor.device)
+        elif tensor.dtype != out.dtype and out.dtype != torch.float32:
+            out = out.float()
+        out[at : at + count].copy_(tensor)
+        at += count
+        del tensor
+    return out
+
+
+def interleaved_rows(weights, gate_name: str, up_name: str, inter: int, block: int) -> torch.Tensor:
+    """``interleave_rows`` of two ``[inter, hidden]`` tensors looked up one after the other
+    and copied straight into the result."""
+    out = None
+    for index, name in enumerate((gate_name, up_name)):
+        tensor = weights[name]
+        if out is None:
+            out = torch.empty((2 * inter, tensor.shape[1]), dtype=tensor.dtype, device=tensor.device)
+        elif tensor.dtype != out.dtype and out.dtype != torch.float32:
+            out = out.float()
+        out.view(inter // block, 2, block, tensor.shape[1])[:, index].copy_(tensor.view(inter // block, block, -1))
+        del tensor
+    return out
+
+
 def interleave_rows(gate: torch.Tensor, up: torch.Tensor, block: int) -> torch.Tensor:
     """Rows [block of gate, block of up, block of gate, ...]; both are [I, H] with I % block == 0."""
     if gate.dtype != up.dtype:
@@ -84,12 +120,3 @@ def interleave_rows(gate: torch.Tensor, up: torch.Tensor, block: int) -> torch.T
     inter, hidden = gate.shape
     stacked = torch.stack((gate.view(inter // block, block, hidden), up.view(inter // block, block, hidden)), dim=1)
     return stacked.reshape(2 * inter, hidden).contiguous()
-
-
-def fuse_rows(tensors: list) -> torch.Tensor:
-    """Concatenate ``[out_i, in]`` matrices (or bias vectors) along rows; if their dtypes
-    differ, all are raised to 32-bit first (exact for bfloat16)."""
-    dtypes = {t.dtype for t in tensors}
-    if len(dtypes) > 1:
-        tensors = [t.float() for t in tensors]
-    return torch.cat(tensors, dim=0).contiguous()

@@ -77,6 +77,20 @@ def _stored_dtype(handle, name: str) -> str:
                 torch.bfloat16: "BF16"}.get(handle.get_tensor(name).dtype, "other")
 
 
+def _all_finite(tensor: torch.Tensor) -> torch.Tensor:
+    """0-d bool tensor on the tensor's device; large tensors are tested in pieces, so that the
+    test's temporaries (an absolute value and masks, several bytes per element) stay small
+    beside the tensor."""
+    flat = tensor.reshape(-1)
+    piece = 1 << 20
+    if flat.numel() <= piece:
+        return torch.isfinite(flat).all()
+    ok = torch.ones((), dtype=torch.bool, device=tensor.device)
+    for begin in range(0, flat.numel(), piece):
+        ok = ok & torch.isfinite(flat[begin : begin + piece]).all()
+    return ok
+
+
 class CheckpointTensors(Mapping):
     """name -> tensor on the device, read from the shard when asked for (and not kept).
 
@@ -107,7 +121,7 @@ class CheckpointTensors(Mapping):
             handle = self._handles[path] = safe_open(str(path), framework="pt", device="cpu").__enter__()
         tensor = _keep_dtype(handle.get_tensor(name), self._dtype).to(self._device)
         if tensor.is_floating_point():
-            self._finite.append((name, torch.isfinite(tensor).all()))
+            self._finite.append((name, _all_finite(tensor)))
         return tensor
 
     def close(self) -> None:

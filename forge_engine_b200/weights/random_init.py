@@ -26,6 +26,8 @@ class RandomTensors(Mapping):
     On the CPU the values are the same on every machine; on a CUDA device they are
     reproducible for that device type only (used for benchmark-sized models)."""
 
+    PIECE = 1 << 20
+
     def __init__(self, expected: dict, seed: int, *, std: float = 0.02, dtype=torch.bfloat16, device="cpu") -> None:
         self._expected = expected
         self._index = {name: i for i, name in enumerate(expected)}
@@ -40,9 +42,16 @@ class RandomTensors(Mapping):
     def __getitem__(self, name: str) -> torch.Tensor:
         info = self._expected[name]
         generator = torch.Generator(device=self.device).manual_seed(self.seed * 1_000_003 + self._index[name])
-        noise = torch.randn(info.shape, generator=generator, dtype=torch.float32, device=self.device)
-        value = noise.mul_(0.1).add_(1.0) if info.role == "norm" else noise.mul_(self.std)
-        return value.to(self.dtype)
+        out = torch.empty(info.shape, dtype=self.dtype, device=self.device)
+        flat = out.view(-1)
+        # drawn in 32-bit in pieces of at most 2^20 values, so that a large table (an embedding)
+        # does not exist a second time in 32-bit while it is drawn
+        for begin in range(0, max(1, flat.numel()), self.PIECE):
+            count = min(self.PIECE, flat.numel() - begin)
+            noise = torch.randn(count, generator=generator, dtype=torch.float32, device=self.device)
+            flat[begin : begin + count] = noise.mul_(0.1).add_(1.0) if info.role == "norm" else noise.mul_(self.std)
+            del noise
+        return out
 
     def close(self) -> None:
         pass

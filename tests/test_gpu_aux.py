@@ -112,7 +112,8 @@ def test_loading_holds_no_second_copy_of_the_weights(native, tmp_path) -> None:
         held = torch.cuda.memory_allocated() - before
         peak = torch.cuda.max_memory_allocated() - before
         weights = runner.model.weight_bytes()
-        assert weights > 150e6 and held < 1.03 * weights
+        # what stays: the weights a step reads, the embedding table (untied here), a tiny cache
+        assert weights > 150e6 and held < 1.10 * weights
         assert peak <= 1.05 * held, f"{build}: peak {peak / 1e6:.1f} MB while loading, {held / 1e6:.1f} MB held"
         del runner
 
