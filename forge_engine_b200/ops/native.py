@@ -484,6 +484,23 @@ def gemm_tc5_set_test_fault(wait_limit: int = 0, skip_kblock: int = -1) -> None:
 TC5_MAX_ROWS = 64   # up to this many rows the tcgen05 kernel is used instead of the library GEMM
 
 
+import os as _os
+
+_ADD_TARGET = int(_os.environ.get("FORGE_ENGINE_ADD_BLOCKS", "288"))
+_ADD_LIMIT = int(_os.environ.get("FORGE_ENGINE_ADD_SPLITS", "16"))
+
+
+def tc5_ksplit_add(o: int, k: int) -> int:
+    """Blocks per 128-feature tile of a product that adds into the residual stream.  Its
+    partial sums meet in memory through atomic adds, so the k-splits need not form a cluster
+    and there may be more of them: about 288 blocks, just under the 296 a B200 holds at once
+    (measured at the 4B shape, batch 8, per decode step: 2.60 ms with 8 splits, 2.53 with 12,
+    2.51 with 14 or 15, 2.72 with 16 - 320 blocks no longer run in one round).  A block keeps
+    at least four 64-wide k-blocks."""
+    tiles = -(-o // 128)
+    return max(1, min(_ADD_LIMIT, round(_ADD_TARGET / tiles), (k // 64) // 4))
+
+
 def tc5_ksplit(o: int, k: int) -> int:
     """Blocks per 128-feature tile for few tokens.  A weight with few tiles is cut along k
     so that about 190 blocks stream it (measured best on a B200: 4 for 48 tiles, 8 for 20);
@@ -567,6 +584,75 @@ def gemm_tc5_qkv_rope(
         ),
         "gemm_tc5_qkv_rope",
     )
+
+
+# ---------------------------------------------------------------------------
+# several dependent projections of a decode step in one persistent kernel
+# ---------------------------------------------------------------------------
+
+CHAIN_SRC_ACTIVATIONS, CHAIN_SRC_NORM = 0, 1
+CHAIN_ADD, CHAIN_SILU_MUL = 0, 1
+CHAIN_MAX_TOKENS = 16
+
+
+class _ChainOp(ctypes.Structure):
+    _fields_ = [("w", c_void_p), ("x", c_void_p), ("norm_w", c_void_p), ("out", c_void_p),
+                ("m", c_int), ("k", c_int), ("src", c_int), ("epi", c_int), ("eps", c_float)]
+
+
+def _chain_ops(ops: list):
+    array = (_ChainOp * len(ops))()
+    for slot, op in zip(array, ops):
+        w = op["w"]
+        slot.w, slot.x, slot.out = ptr(w), ptr(op["x"]), ptr(op["out"])
+        slot.norm_w = ptr(op.get("norm_w"))
+        slot.m, slot.k = int(w.shape[0]), int(w.shape[1])
+        slot.src, slot.epi, slot.eps = int(op["src"]), int(op["epi"]), float(op.get("eps", 0.0))
+    return array
+
+
+def decode_chain_takes(shapes: list, n: int) -> bool:
+    """Whether ``decode_chain`` takes projections of these ``(m, k, src, epi)`` for ``n`` tokens."""
+    array = (_ChainOp * len(shapes))()
+    for slot, (m, k, src, epi) in zip(array, shapes):
+        slot.m, slot.k, slot.src, slot.epi = int(m), int(k), int(src), int(epi)
+    fn = lib().fe_decode_chain_check
+    fn.argtypes = [ctypes.POINTER(_ChainOp), c_int, c_int]
+    fn.restype = c_int
+    return fn(array, len(shapes), int(n)) == 0
+
+
+def decode_chain(ops: list, n: int, status: torch.Tensor) -> None:
+    """Up to three projections, each reading what the one before wrote, in one launch.
+
+    Every op is a dict: ``w`` bfloat16 [m, k]; ``src`` CHAIN_SRC_ACTIVATIONS with ``x`` bfloat16
+    [n, k], or CHAIN_SRC_NORM with ``x`` the 32-bit residual stream [n, k], ``norm_w`` [k] and
+    ``eps`` (the operand is then rmsnorm(x) * norm_w); ``epi`` CHAIN_ADD with ``out`` 32-bit
+    [n, m] that the product is added to, or CHAIN_SILU_MUL with ``out`` bfloat16 [n, m / 2] for
+    a weight whose rows alternate 16 gate and 16 up features.  ``n`` <= 16 tokens."""
+    for op in ops:
+        w, x, out = _dense(op["w"], "w"), _dense(op["x"], "x"), _dense(op["out"], "out")
+        m, k = w.shape
+        assert w.dtype == torch.bfloat16 and x.shape == (n, k)
+        if op["src"] == CHAIN_SRC_NORM:
+            norm_w = _dense(op["norm_w"], "norm_w")
+            assert x.dtype == torch.float32 and norm_w.dtype == torch.float32 and norm_w.numel() == k
+        else:
+            assert x.dtype == torch.bfloat16
+        if op["epi"] == CHAIN_ADD:
+            assert out.dtype == torch.float32 and out.shape == (n, m)
+        else:
+            assert out.dtype == torch.bfloat16 and out.shape == (n, m // 2)
+    handle = lib()
+    handle.fe_decode_chain_counters.restype = c_int
+    handle.fe_decode_chain_staging.restype = c_int
+    device = ops[0]["w"].device
+    counters = _scratch.get("chain counters", device, handle.fe_decode_chain_counters(), torch.int32, 0, zero=True)
+    staging = _scratch.get("chain staging", device, handle.fe_decode_chain_staging(), torch.float32, 0, zero=True)
+    fn = handle.fe_decode_chain
+    fn.argtypes = [ctypes.POINTER(_ChainOp), c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    fn.restype = c_int
+    check(fn(_chain_ops(ops), len(ops), int(n), ptr(counters), ptr(staging), ptr(status), stream()), "decode_chain")
 
 
 def sample(

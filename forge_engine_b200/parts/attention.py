@@ -190,6 +190,20 @@ class GQAttention(Mixer):
         return self._slots
 
     def forward(self, x, batch, cache: CacheView):
+        out = self.attend(x, batch, cache)
+        with self.ctx.section("mixer.o_proj"):
+            return self.o_proj(out)
+
+    def forward_add(self, x, batch, cache: CacheView, residual) -> bool:
+        """``forward`` with the update added into the 32-bit ``residual`` by the output
+        projection itself.  False (and nothing done) where that projection cannot."""
+        if not self.o_proj.adds_into(x, residual) or self.ctx.timer is not None:
+            return False
+        return self.o_proj.add_into(self.attend(x, batch, cache), residual)
+
+    def attend(self, x, batch, cache: CacheView):
+        """Everything but the output projection: the heads' outputs [N, heads * head_dim]
+        (a block that fuses ``o_proj`` with what follows takes them from here)."""
         with self.ctx.section("mixer.qkv_rope_cache"):
             qkv = self._project(x, batch, cache)
         k_cache, v_cache = cache.kv
@@ -204,8 +218,7 @@ class GQAttention(Mixer):
                     qkv, qkv.shape[1], k_cache, v_cache, table, batch.positions, batch.token_entry,
                     self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
                 )
-        with self.ctx.section("mixer.o_proj"):
-            return self.o_proj(out)
+        return out
 
     def _project(self, x, batch, cache: CacheView):
         """q, k, v of the step's tokens: projected, normalised per head, rotated; k and v

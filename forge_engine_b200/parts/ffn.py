@@ -40,6 +40,14 @@ class GatedMLP(FeedForward):
             "down_proj.weight": WeightInfo((h, i)),
         }
 
+    def forward_add(self, x, residual) -> bool:
+        """``forward`` with the update added into the 32-bit ``residual`` by the down projection
+        itself.  False (and nothing done) where that projection cannot."""
+        if not (self.block == 16 and self.down.adds_into(x, residual) and self.gate_up._tc5_ok(x)
+                and self.gate_up.out_features % 32 == 0 and self.gate_up.bias is None):
+            return False
+        return self.down.add_into(self.gate_up.silu_mul(x, self.block), residual)
+
     def forward(self, x):
         act = self.gate_up.silu_mul(x, self.block) if self.block else None
         if act is None:

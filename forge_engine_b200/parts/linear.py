@@ -10,6 +10,8 @@ Which kernel runs is decided by the dtypes alone:
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import native
@@ -64,6 +66,20 @@ class Linear:
         native.gemm_simt(x, self.weight, out, self.bias)
         return out
 
+
+    def adds_into(self, x: torch.Tensor, residual: torch.Tensor) -> bool:
+        """Whether ``add_into`` works for an input with ``x``'s dtype and row count."""
+        return (self._tc5_ok(x) and residual.dtype == torch.float32 and residual.is_contiguous()
+                and os.environ.get("FORGE_ENGINE_ADD_EPILOGUE", "1") != "0")
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor) -> bool:
+        """residual (32-bit [n, out]) += x W^T in the product's own epilogue, if the tcgen05
+        kernel takes the call (then True); otherwise nothing happens."""
+        if not self.adds_into(x, residual):
+            return False
+        native.gemm_tc5(x, self.weight, residual, native.TC5_ADD_F32, self.status, bias=self.bias,
+                        ksplit=native.tc5_ksplit_add(self.out_features, self.in_features))
+        return True
 
     def silu_mul(self, x: torch.Tensor, interleave: int) -> torch.Tensor | None:
         """For a weight whose rows alternate ``interleave`` gate and up features: returns

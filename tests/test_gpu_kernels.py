@@ -590,3 +590,54 @@ def test_gemm_tc5_silu_mul(native, n, inter, k, ksplit) -> None:
     native.gemm_tc5(x, w, out, native.TC5_SILU_MUL, status, ksplit=ksplit)
     torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=1e-2)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("n,hidden,heads,inter", [(1, 64, 64, 128), (8, 2560, 4096, 9728), (16, 2560, 4096, 9728),
+                                                  (5, 200, 136, 304), (13, 1024, 768, 19200), (3, 2048, 2048, 6144),
+                                                  (2, 72, 96, 48)])
+def test_decode_chain(native, n, hidden, heads, inter) -> None:
+    """Output projection (+= residual), RMS norm + gate/up with SiLU*mul, down projection
+    (+= residual) as one persistent kernel, against the same steps in 64-bit from the same
+    bfloat16 inputs: sizes with fewer tiles than blocks, with more (whole tiles and shares of
+    the left-over ones), widths that are no multiple of a tile, and two launches in a row (the
+    second finds counters and staging tiles zeroed again)."""
+    from forge_engine_b200.parts.linear import interleave_rows
+
+    eps = 2e-6
+    g = torch.Generator().manual_seed(n + hidden)
+    x = torch.randn((n, heads), generator=g).bfloat16()
+    w_o = (torch.randn((hidden, heads), generator=g) * heads ** -0.5).bfloat16()
+    w_gate = (torch.randn((inter, hidden), generator=g) * hidden ** -0.5).bfloat16()
+    w_up = (torch.randn((inter, hidden), generator=g) * hidden ** -0.5).bfloat16()
+    w_down = (torch.randn((hidden, inter), generator=g) * inter ** -0.5).bfloat16()
+    norm_w = 1 + 0.1 * torch.randn(hidden, generator=g)
+    h0 = torch.randn((n, hidden), generator=g)
+    shapes = [(hidden, heads, native.CHAIN_SRC_ACTIVATIONS, native.CHAIN_ADD),
+              (2 * inter, hidden, native.CHAIN_SRC_NORM, native.CHAIN_SILU_MUL),
+              (hidden, inter, native.CHAIN_SRC_ACTIVATIONS, native.CHAIN_ADD)]
+    assert native.decode_chain_takes(shapes, n)
+    h1 = h0.double() + x.double() @ w_o.double().t()
+    normed = (h1 * torch.rsqrt(h1.square().mean(-1, keepdim=True) + eps) * norm_w.double()).bfloat16().double()
+    gate, up = normed @ w_gate.double().t(), normed @ w_up.double().t()
+    act_ref = (torch.nn.functional.silu(gate) * up)
+    h2 = h1 + act_ref.bfloat16().double() @ w_down.double().t()
+    w_gu = interleave_rows(w_gate, w_up, 16).to(DEV)
+    status = status_word()
+    for _ in range(2):
+        h = h0.clone().to(DEV)
+        act = torch.full((n, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+        native.decode_chain(
+            [dict(w=w_o.to(DEV), x=x.to(DEV), out=h, src=native.CHAIN_SRC_ACTIVATIONS, epi=native.CHAIN_ADD),
+             dict(w=w_gu, x=h, norm_w=norm_w.to(DEV), eps=eps, out=act, src=native.CHAIN_SRC_NORM, epi=native.CHAIN_SILU_MUL),
+             dict(w=w_down.to(DEV), x=act, out=h, src=native.CHAIN_SRC_ACTIVATIONS, epi=native.CHAIN_ADD)],
+            n, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        torch.testing.assert_close(act.double().cpu(), act_ref, atol=2e-2, rtol=1e-2)
+        # the residual: 32-bit sums of bfloat16 products; the bfloat16 rounding of the operands in
+        # between (norm output, activation) may fall the other way than in the 64-bit restatement
+        torch.testing.assert_close(h.double().cpu(), h2, atol=2e-2, rtol=1e-2)
+    assert native.damaged_canaries() == []
+    # what it does not take: more than 16 tokens, a norm wider than its operand buffer
+    assert not native.decode_chain_takes(shapes, 17)
+    assert not native.decode_chain_takes([(256, 4096, native.CHAIN_SRC_NORM, native.CHAIN_ADD)], 4)
