@@ -53,6 +53,10 @@ class StepBatch:
     max_new: int = 0
     max_ctx: int = 0
     shared: dict = field(default_factory=dict)
+    # What parts decide on the host for this step, by a key of their own (see
+    # ``plan_step`` of the model); filled before a step is captured in a CUDA graph, so that
+    # the replayed kernels are the ones the step's real entries call for.
+    plans: dict = field(default_factory=dict)
 
 
 @dataclass
@@ -70,15 +74,16 @@ class BatchPlan:
     max_ctx: int
 
 
-def plan_batch(entries: Sequence[StepEntry], cache, *, pad_entries: int = 0, table_width: int | None = None,
+def plan_batch(entries: Sequence[StepEntry], cache, *, pad_counts: Sequence[int] = (), table_width: int | None = None,
                null_page: int | None = None, null_slot: int = 0) -> BatchPlan:
     """Lay out the step's integers.  Pages for the new tokens must already be reserved.
 
-    ``pad_entries`` appends that many filler entries (one token at position 0 whose keys
-    go to ``null_page``, a page no request ever holds, and whose state slot is
-    ``null_slot``, a row no request ever holds) so that the batch has a fixed
-    number of entries; ``table_width`` fixes the width of every block table.  Both are
-    used by replayed CUDA graphs, whose kernels are launched with fixed sizes."""
+    ``pad_counts`` appends one filler entry per element, with that many tokens at
+    positions 0.. of a request that holds only ``null_page`` (a page no request ever holds;
+    its keys land there) and whose state slot is ``null_slot`` (a row no request ever
+    holds), so that the batch has a fixed number of entries and of tokens; ``table_width``
+    fixes the width of every block table.  Both are used by replayed CUDA graphs, whose
+    kernels are launched with fixed sizes."""
     token_ids: list[int] = []
     positions: list[int] = []
     token_entry: list[int] = []
@@ -102,14 +107,15 @@ def plan_batch(entries: Sequence[StepEntry], cache, *, pad_entries: int = 0, tab
         ctx_lens.append(start + count)
         slots.append(request.slot)
         host.append((request.slot, start, count))
-    for pad in range(pad_entries):
-        token_ids.append(0)
-        positions.append(0)
-        token_entry.append(len(entries) + pad)
-        want_rows.append(cu[-1])
-        cu.append(cu[-1] + 1)
+    pad_entries = len(pad_counts)
+    for pad, count in enumerate(pad_counts):
+        token_ids.extend([0] * count)
+        positions.extend(range(count))
+        token_entry.extend([len(entries) + pad] * count)
+        want_rows.append(cu[-1] + count - 1)
+        cu.append(cu[-1] + count)
         starts.append(0)
-        ctx_lens.append(1)
+        ctx_lens.append(count)
         slots.append(null_slot)
     n, r = cu[-1], len(entries) + pad_entries
     tables = []
@@ -124,9 +130,12 @@ def plan_batch(entries: Sequence[StepEntry], cache, *, pad_entries: int = 0, tab
             pages = req.tables[g].pages
             rows.extend(pages)
             rows.extend([-1] * (width - len(pages)))
-        for _ in range(pad_entries):
-            rows.append(null_page)
-            rows.extend([-1] * (width - 1))
+        for count in pad_counts:
+            pages = -(-count // cache.page_size)
+            if pages > width:
+                raise ValueError("a filler entry needs a wider block table")
+            rows.extend([null_page] * pages)
+            rows.extend([-1] * (width - pages))
         tables.append((width, rows))
     flat: list[int] = []
     offsets = {}
@@ -147,7 +156,7 @@ def plan_batch(entries: Sequence[StepEntry], cache, *, pad_entries: int = 0, tab
     for g, (_, rows) in enumerate(tables):
         put(f"table{g}", rows)
     return BatchPlan(flat, offsets, n, r, len(want_rows), [w for w, _ in tables], host,
-                     max((c for _, _, c in host), default=1), max(ctx_lens))
+                     max([c for _, _, c in host] + list(pad_counts), default=1), max(ctx_lens))
 
 
 def batch_from_buffer(plan: BatchPlan, device_buffer: torch.Tensor) -> StepBatch:

@@ -1,13 +1,24 @@
-"""CUDA graphs for decode steps.
+"""CUDA graphs for the steps that are too short to be launched kernel by kernel.
 
-A decode step at small batch is a few hundred short kernels; issued one by one from
-Python they take longer to launch than to run.  Upstream launches everything eagerly and
-even synchronises per token (src/forge_engine/engine.py:425).  Here a step in which every
-entry brings exactly one token is captured once per *bucket* - (entries rounded up to a
-power of two, block-table width rounded up to a power of two) - and replayed: the
-step's integers are copied into the graph's fixed device buffer, filler entries pad the
-batch to the bucket's size (their keys go to the cache's null page), and the kernels run
-with the sizes they were captured with.
+A decode step at small batch is a few hundred short kernels, and so is a step that mixes
+a few prompt portions with decoded tokens under a small token budget; issued one by one from
+Python they take longer to launch (about 4 ms for 36 layers) than to run.  Upstream launches
+everything eagerly and even synchronises per token (src/forge_engine/engine.py:425).  Here a
+step is captured once per *bucket* and replayed:
+
+* the bucket fixes the sizes the kernels are launched with: the number of entries (a power
+  of two), the number of tokens (entries for a decode step; else a multiple of 32 up to 256,
+  of 64 beyond), the width of the block tables (a power of two), and what the model's parts
+  decided on the host for this step (``model.plan_step``: for attention, which kernels run and
+  with how many splits);
+* the step's integers are copied into the graph's fixed device buffer; filler entries pad the
+  batch to the bucket's sizes (their tokens sit at positions 0.. of a request that holds only
+  the cache's null page, their state is the null slot), and nobody reads their rows;
+* every entry is laid out as wanting the logits of its last token, so that the layout does
+  not depend on which entries do.
+
+Steps of more than ``MAX_GRAPH_TOKENS`` tokens keep the GPU busy for longer than they take to
+launch and run eagerly, as do steps that want logits elsewhere than at an entry's last token.
 """
 
 from __future__ import annotations
@@ -15,7 +26,9 @@ from __future__ import annotations
 import torch
 
 from ..ops import native
-from .batch import BatchPlan, batch_from_buffer, plan_batch
+from .batch import BatchPlan, StepEntry, batch_from_buffer, plan_batch
+
+MAX_GRAPH_TOKENS = 512
 
 
 def _bucket(value: int, floor: int = 1) -> int:
@@ -23,6 +36,11 @@ def _bucket(value: int, floor: int = 1) -> int:
     while size < value:
         size *= 2
     return size
+
+
+def _token_bucket(tokens: int) -> int:
+    step = 32 if tokens <= 256 else 64
+    return -(-tokens // step) * step
 
 
 class _CapturedStep:
@@ -55,7 +73,7 @@ class _CapturedStep:
 
 
 class DecodeGraphs:
-    """Captures and replays decode steps of one ModelRunner."""
+    """Captures and replays short steps of one ModelRunner."""
 
     def __init__(self, model, cache, max_entries: int) -> None:
         self.model = model
@@ -69,23 +87,53 @@ class DecodeGraphs:
         their parts); a model that does not say is run eagerly."""
         return bool(getattr(self.model, "graph_safe", False))
 
-    def _plan(self, entries, bucket_entries: int, width: int, spread: int = 1) -> BatchPlan:
-        return plan_batch(entries, self.cache, pad_entries=bucket_entries - len(entries), table_width=width,
+    def takes(self, entries) -> bool:
+        """Whether this step is replayed from a graph: few tokens, and logits wanted at an
+        entry's last token or not at all."""
+        tokens = 0
+        for entry in entries:
+            count = len(entry.tokens)
+            tokens += count
+            want = list(entry.want)
+            if want and want != [count - 1]:
+                return False
+        return tokens == len(entries) or tokens <= MAX_GRAPH_TOKENS
+
+    # -- sizes ---------------------------------------------------------------------
+    def _shape(self, entries) -> tuple:
+        """(entries, tokens, filler token counts) of the bucket this step runs in."""
+        real_entries, real_tokens = len(entries), sum(len(e.tokens) for e in entries)
+        if real_tokens == real_entries:                          # one token each: a decode step
+            bucket_entries = min(_bucket(real_entries), _bucket(self.max_entries))
+            return bucket_entries, bucket_entries, [1] * (bucket_entries - real_entries)
+        bucket_tokens = _token_bucket(real_tokens)
+        bucket_entries = _bucket(real_entries + (1 if bucket_tokens > real_tokens else 0))
+        fillers = bucket_entries - real_entries
+        if fillers > bucket_tokens - real_tokens:                # every filler entry brings a token
+            bucket_tokens = _token_bucket(real_tokens + fillers)
+        spare = bucket_tokens - real_tokens
+        counts = [spare - (fillers - 1)] + [1] * (fillers - 1) if fillers else []
+        return bucket_entries, bucket_tokens, counts
+
+    def _plan(self, entries, fillers: list, width: int) -> BatchPlan:
+        return plan_batch(entries, self.cache, pad_counts=fillers, table_width=width,
                           null_page=self.cache.null_page, null_slot=self.cache.null_slot)
 
     def _capture(self, key: tuple) -> _CapturedStep:
-        bucket_entries, width, spread = key
+        bucket_entries, bucket_tokens, width, plans = key
         device = self.model.ctx.device
-        page = self.cache.page_size
         # A batch of filler entries only: it has the bucket's layout and is safe to run.
-        plan = self._plan([], bucket_entries, width)
-        # The capture sees host-side entries that stand for every step that will be replayed
-        # with this graph, so that size decisions made on the host (attention splits) fit
-        # them: one entry at the bucket's longest context, the others `spread` times shorter.
-        plan.entries = [(0, width * page - 1, 1)] + [(0, max(1, width * page // spread) - 1, 1)] * (bucket_entries - 1)
-        plan.max_ctx = width * page
+        if bucket_tokens == bucket_entries:
+            fillers = [1] * bucket_entries
+        else:
+            fillers = [bucket_tokens - (bucket_entries - 1)] + [1] * (bucket_entries - 1)
+        plan = self._plan([], fillers, width)
+        assert plan.n_tokens == bucket_tokens and plan.n_entries == bucket_entries
+        if bucket_tokens != bucket_entries:
+            plan.max_new = bucket_tokens        # no entry brings more; kernels sized by it skip what is not there
         buffer = torch.tensor(plan.flat, dtype=torch.int32).to(device)
         batch = batch_from_buffer(plan, buffer)
+        batch.plans = dict(plans)               # what the parts decided on the host for the steps of this bucket
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):
@@ -102,29 +150,31 @@ class DecodeGraphs:
         return _CapturedStep(graph, buffer, logits, native.LAUNCHES - before)
 
     def run(self, entries, device_tokens: tuple | None = None) -> torch.Tensor:
-        """Replay the step for ``entries`` (one token each; pages already reserved).
-        Returns logits for the entries that want them, in entry order.  With
-        ``device_tokens = (tensor, rows)`` entry i's token is ``tensor[rows[i]]``, copied
-        on the device after the step's other integers have been uploaded."""
-        bucket_entries = min(_bucket(len(entries)), _bucket(self.max_entries))
+        """Replay the step for ``entries`` (pages already reserved).  Returns logits for the
+        entries that want them, in entry order.  With ``device_tokens = (tensor, rows)`` (steps
+        of one token per entry only) entry i's token is ``tensor[rows[i]]``, copied on the
+        device after the step's other integers have been uploaded."""
+        bucket_entries, bucket_tokens, fillers = self._shape(entries)
         widest = max(
             (len(self.cache.request(e.key).tables[g].pages) for e in entries for g in range(len(self.cache.groups))),
             default=1,
         )
-        # how much longer the longest context is than the average one (a power of two, rounded down)
-        pages = [max((len(t.pages) for t in self.cache.request(e.key).tables), default=0) for e in entries]
-        spread = 1
-        while spread < 32 and widest * len(pages) >= 2 * spread * max(1, sum(pages)):
-            spread *= 2
-        key = (bucket_entries, _bucket(widest, 8), spread)
-        # every entry is laid out as wanting its token, so that the layout is fixed
+        widest = max(widest, -(-max(fillers, default=1) // self.cache.page_size))
+        width = _bucket(widest, 8)
+        # what the parts decide on the host from the step's real entries (attention: which
+        # kernels, how many splits) belongs to the bucket: a graph holds one such decision
+        host = [(self.cache.request(e.key).slot, self.cache.request(e.key).length, len(e.tokens)) for e in entries]
+        planner = getattr(self.model, "plan_step", None)
+        plans = planner(host, self.cache.page_size) if planner is not None else {}
+        key = (bucket_entries, bucket_tokens, width, tuple(sorted(plans.items(), key=repr)))
+        # every entry is laid out as wanting its last token, so that the layout is fixed
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
-        full = [type(e)(e.key, e.tokens, [0]) for e in entries]
+        full = [StepEntry(e.key, e.tokens, [len(e.tokens) - 1]) for e in entries]
         step = self.captured.get(key)
         if step is None:
             step = self._capture(key)
             self.captured[key] = step
-        plan = self._plan(full, *key)
+        plan = self._plan(full, fillers, width)
         assert len(plan.flat) == step.buffer.numel()
         step.upload(plan.flat)
         if device_tokens is not None:

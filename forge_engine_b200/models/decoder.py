@@ -86,6 +86,17 @@ class DecoderModel:
         return (all(getattr(block, "graph_safe", False) for block in self.blocks)
                 and getattr(self.final_norm, "graph_safe", False))
 
+    def plan_step(self, entries: list, page_size: int) -> dict:
+        """What the blocks' parts decide on the host for a step of these entries
+        (``(slot, tokens cached, new tokens)`` each): {part's key: its decision}.  A step is
+        captured in a CUDA graph once per distinct answer."""
+        plans: dict = {}
+        for block in self.blocks:
+            planner = getattr(block, "plan_step", None)
+            if planner is not None:
+                planner(entries, page_size, plans)
+        return plans
+
     # -- cache ---------------------------------------------------------------------
     def cache_needs(self) -> tuple:
         """(needs per run, {run: run whose cache it reads})."""

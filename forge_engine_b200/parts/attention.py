@@ -154,6 +154,7 @@ class GQAttention(Mixer):
             self.k_norm = weights["k_norm.weight"].float().contiguous()
         self.position = build_part(spec.position, {}, ctx)
         self._slots = None
+        self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window)
         self.last_splits = None   # what the last step's decode entries ran with (0: balanced kernel)
 
     @classmethod
@@ -262,13 +263,19 @@ class GQAttention(Mixer):
                 and x.shape[0] <= FUSED_PROJECTION_ROWS and self.qkv_proj._tc5_ok(x)
                 and os.environ.get("FORGE_ENGINE_FUSED_QKV", "1") != "0")
 
-    def _tensor_core_attention(self, qkv, k_cache, v_cache, table, batch, out, groups) -> None:
-        """Entries with few rows (new tokens x heads per kv head <= 16) take the split
-        decode kernel, the rest the prefill kernel; both may run in one step."""
+    def plan_step(self, entries: list, page_size: int, plans: dict) -> None:
+        """The host's decision for a step of ``entries`` ((slot, cached, new) each): entries
+        with few rows (new tokens x heads per kv head <= 16) take the split decode kernel, the
+        rest the prefill kernel; both may run in one step.  (run prefill, run decode, splits
+        of the decode kernel - 0: the kernel that spreads all tiles evenly) under this
+        mixer's key; layers with the same geometry share it."""
+        if self.ctx.dtype != torch.bfloat16 or self.plan_key in plans:
+            return
+        groups = self.nq // self.nkv
         limit = native.ATTN_DECODE_ROWS
-        small = [(start, count) for _, start, count in batch.entries if count * groups <= limit]
+        small = [(start, count) for _, start, count in entries if count * groups <= limit]
         run_decode = bool(small)
-        run_prefill = len(small) < batch.n_entries
+        run_prefill = len(small) < len(entries)
         splits = 1
         if run_decode:
             contexts = [start + count for start, count in small]
@@ -277,10 +284,17 @@ class GQAttention(Mixer):
             # FORGE_ENGINE_DECODE_BALANCED: 0 never uses the balanced kernel, "always" uses it
             # wherever it can run, anything else lets the estimate decide
             wish = os.environ.get("FORGE_ENGINE_DECODE_BALANCED", "1")
-            balanced = (self.d % 64 == 0 and k_cache.shape[2] <= 64 and 64 % k_cache.shape[2] == 0
-                        and batch.n_entries <= BALANCED_MAX_ENTRIES and wish != "0")
+            balanced = (self.d % 64 == 0 and page_size <= 64 and 64 % page_size == 0
+                        and len(entries) <= BALANCED_MAX_ENTRIES and wish != "0")
             splits = 0 if balanced and wish == "always" else choose_splits(
                 [-(-c // 64) for c in contexts], self.nkv, balanced, self.decode_slots())
+        plans[self.plan_key] = (run_prefill, run_decode, splits)
+
+    def _tensor_core_attention(self, qkv, k_cache, v_cache, table, batch, out, groups) -> None:
+        if self.plan_key not in batch.plans:
+            self.plan_step(batch.entries, k_cache.shape[2], batch.plans)
+        run_prefill, run_decode, splits = batch.plans[self.plan_key]
+        if run_decode:
             self.last_splits = splits
         native.attention_mma(
             qkv, qkv.shape[1], k_cache, v_cache, table, batch.cu_tokens, batch.starts,

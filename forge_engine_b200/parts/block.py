@@ -36,6 +36,11 @@ class PreNormBlock:
     def cache_needs(self):
         return self.mixer.cache_needs()
 
+    def plan_step(self, entries: list, page_size: int, plans: dict) -> None:
+        planner = getattr(self.mixer, "plan_step", None)
+        if planner is not None:
+            planner(entries, page_size, plans)
+
     @property
     def graph_safe(self) -> bool:
         return all(getattr(part, "graph_safe", False)

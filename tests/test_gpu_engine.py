@@ -941,6 +941,68 @@ def test_graph_replay_equals_eager_steps(fe, dtype, tmp_path) -> None:
                 assert torch.equal(eager, replayed)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "E"])
+def test_mixed_steps_replayed_from_graphs_equal_eager_steps(fe, dtype, name, tmp_path) -> None:
+    """Steps that mix prompt portions with decoded tokens are replayed from CUDA graphs too
+    (token and entry counts padded to a bucket with filler entries on the null page): the same
+    schedule launched eagerly gives the same logits - the same bits in 32-bit - and both agree
+    with the plain implementation.  Configuration E has a windowed layer group and head size 64."""
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+
+    raw, seed = {"C": (plain.TINY_C, 5), "E": (plain.TINY_E, 7)}[name]
+    cfg, weights = make_model_folder(tmp_path / "m", raw, seed)
+    ids = {k: random_ids(cfg.vocab_size, n, 60 + n) for k, n in (("a", 140), ("b", 55), ("c", 97), ("d", 23))}
+    prompt = {"a": 120, "b": 30, "c": 80, "d": 20}
+    portion = (7, 33, 2, 18, 40, 5)
+    results = {}
+    for graphs in (False, True):
+        runner = ModelRunner.from_folder(tmp_path / "m", dtype=dtype, page_size=8, num_pages=96, max_requests=4,
+                                         use_graphs=graphs)
+        rows = {k: [] for k in ids}
+        fed = {k: 0 for k in ids}
+        live, waiting = [], ["a", "b", "c", "d"]
+        step = 0
+        while live or waiting:
+            if waiting and step % 2 == 0:
+                key = waiting.pop(0)
+                runner.begin(key)
+                live.append(key)
+            entries = []
+            for i, k in enumerate(live):
+                if fed[k] < prompt[k]:
+                    n = min(portion[(step + i) % len(portion)], prompt[k] - fed[k])
+                    want = [n - 1] if fed[k] + n == prompt[k] else []
+                else:
+                    n, want = 1, [0]
+                entries.append(StepEntry(k, ids[k][fed[k] : fed[k] + n], want))
+            out = runner.step(entries).cpu()
+            row = 0
+            for e in entries:
+                if e.want:
+                    rows[e.key].append((fed[e.key] + len(e.tokens) - 1, out[row].clone()))
+                    row += 1
+                fed[e.key] += len(e.tokens)
+            for k in [k for k in live if fed[k] == len(ids[k])]:
+                runner.end(k)
+                live.remove(k)
+            step += 1
+        runner.check_status()
+        assert all(n == 0 for n in runner.cache.leased_pages())
+        if graphs:
+            mixed = [key for key in runner.graphs.captured if key[0] != key[1]]
+            assert len(mixed) >= 3, list(runner.graphs.captured)      # several buckets of mixed steps were captured
+        results[graphs] = rows
+    for k in ids:
+        ref = plain.forward_logits(ids[k], weights, cfg)
+        assert len(results[True][k]) == len(results[False][k]) >= len(ids[k]) - prompt[k]
+        for (pos_e, eager), (pos_g, replayed) in zip(results[False][k], results[True][k]):
+            assert pos_e == pos_g
+            torch.testing.assert_close(replayed, ref[pos_g], **bound(dtype, ref))
+            if dtype == "float32":
+                assert torch.equal(eager, replayed)
+
+
 def test_lookahead_gives_the_same_tokens_as_synchronous_steps(fe, tmp_path) -> None:
     """Decode steps launched one ahead (tokens fed on the device, events one step late)
     against fully synchronous scheduling: same outputs, greedy and sampled, with requests
