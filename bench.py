@@ -206,10 +206,18 @@ def reference_arm(args) -> int:
             "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic token ids (seed 5), upstream model class with torch default init (seed 0)",
             "config": {"model": "Qwen3-4B shape", "layers": raw["num_hidden_layers"], "layers_full": CONFIG_4B["num_hidden_layers"],
-                       "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE,
-                       "api": "ConcurrentGenerationEngine.step with a stub tokenizer"},
+                       "hidden": raw["hidden_size"], "q_heads": raw["num_attention_heads"],
+                       "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
+                       "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+                       "global_batch": batch, "seq_len": CONTEXT, "max_context": raw["max_position_embeddings"],
+                       "page_size": PAGE, "tied_embeddings": True, "parallelism": "single GPU",
+                       "l2": "inputs larger than L2 (weights 8.0 GB read every step)", "peaks": peaks()[2]},
+            "api": "ConcurrentGenerationEngine.step with a stub tokenizer",
             "clocks": clocks,
-            "e2e": {"value": round(batch * steps / wall, 2), "unit": "tokens/s", "ms_per_step": round(1e3 * wall / steps, 4)},
+            # upstream keeps the pending token on the device and reads every request's sampled id
+            # back with .item() (an int64 each, src/forge_engine/scheduler.py:472-482)
+            "e2e": {"value": round(batch * steps / wall, 2), "unit": "tokens/s", "ms_per_step": round(1e3 * wall / steps, 4),
+                    "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8 * batch},
         }))
         return 0
     except Exception as error:  # the arm must never fail the run
@@ -461,19 +469,20 @@ def main() -> int:
     steps_total = args.warmup + args.steps + 64 + 16
     pages_per_request = -(-(CONTEXT + steps_total) // PAGE) + 1
     num_pages = max_batch * pages_per_request + 8
-    runner = ModelRunner.from_random(raw, 0, dtype="bfloat16", device=device, page_size=PAGE,
-                                     num_pages=num_pages, max_requests=max_batch)
+    runner = main_runner = ModelRunner.from_random(raw, 0, dtype="bfloat16", device=device, page_size=PAGE,
+                                                   num_pages=num_pages, max_requests=max_batch)
     for group in runner.cache.groups:        # contexts: pages of random numbers
         group.storage.normal_(0.0, 1.0)
     weight_bytes = runner.model.weight_bytes()
     kv_bytes_per_token = runner.cache.bytes_per_token()
 
-    def decode_run(batch: int, steps: int, warmup: int) -> tuple:
+    def decode_run(batch: int, steps: int, warmup: int, context: int = CONTEXT, runner=None) -> tuple:
+        runner = runner or main_runner
         keys = [f"d{batch}-{i}" for i in range(batch)]
         for key in keys:
             runner.begin(key)
-            runner.cache.reserve(key, CONTEXT)
-            runner.cache.advance(key, CONTEXT)
+            runner.cache.reserve(key, context)
+            runner.cache.advance(key, context)
         tokens = torch.randint(0, raw["vocab_size"], (batch,), generator=gen).tolist()
 
         def one_step():
@@ -499,6 +508,40 @@ def main() -> int:
         for key in keys:
             runner.end(key)
         return ms, clocks, launches
+
+    def mixed_run(tokens: int, decoders: int, steps: int, warmup: int) -> dict:
+        """A step as the scheduler makes it under a token budget of ``tokens``: ``decoders``
+        requests with 2,048-token contexts decode one token each beside a prompt portion of
+        the remaining tokens (the first portion of a fresh request, every step).  Wall time
+        per step - host work, launch and the device, synchronised every step - beside the
+        device time alone: replayed from a CUDA graph the two are about the same."""
+        keys = [f"m{i}" for i in range(decoders)]
+        for key in keys:
+            runner.begin(key)
+            runner.cache.reserve(key, CONTEXT)
+            runner.cache.advance(key, CONTEXT)
+        ids = torch.randint(0, raw["vocab_size"], (decoders,), generator=gen).tolist()
+        portion = torch.randint(0, raw["vocab_size"], (tokens - decoders,), generator=gen).tolist()
+        wall, dev = [], []
+        for i in range(warmup + steps):
+            key = f"mp{i}"
+            runner.begin(key)
+            entries = [StepEntry(k, [t], [0]) for k, t in zip(keys, ids)] + [StepEntry(key, portion, [])]
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            begin.record()
+            runner.step(entries)
+            end.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                wall.append((time.perf_counter() - t0) * 1e3)
+                dev.append(begin.elapsed_time(end))
+            runner.end(key)
+        runner.check_status()
+        for key in keys:
+            runner.end(key)
+        return {"ms_wall": statistics.median(wall), "ms_device": statistics.median(dev)}
 
     def prefill_run(repeats: int) -> dict:
         """One 2,048-token prompt in one step, logits at its last place."""
@@ -616,13 +659,34 @@ def main() -> int:
         for batch in (1, 64):
             ms, _, _ = decode_run(batch, max(10, args.steps // 2), args.warmup)
             points[f"decode_b{batch}"] = round(batch / (ms / 1e3), 2)
+        mixed = mixed_run(256, 8, 20, 5)
+        points["mixed_256"] = round(256 / (mixed["ms_wall"] / 1e3), 1)         # tokens a second, wall clock
+        points["mixed_256_ms_wall"] = round(mixed["ms_wall"], 3)
+        points["mixed_256_ms_device"] = round(mixed["ms_device"], 3)
         record["points"] = points
 
         record["prefill"] = prefill_run(3)
 
-        # end to end through the Python entry point: host ids in, sampled ids out, every step
-        del runner
+        # decode at longer contexts (the model's own position limit, 262,144, instead of the
+        # benchmark's 8,192): 8,192 and 32,768 cached tokens per request, batch 1 and 8
+        del runner, main_runner
         torch.cuda.empty_cache()
+        long_raw = dict(raw, max_position_embeddings=262144)
+        long_steps = 30
+        long_runner = ModelRunner.from_random(long_raw, 0, dtype="bfloat16", device=device, page_size=PAGE,
+                                              num_pages=8 * (-(-(32768 + 64) // PAGE) + 1) + 8, max_requests=8)
+        for group in long_runner.cache.groups:
+            group.storage.normal_(0.0, 1.0)
+        for context, label in ((8192, "8k"), (32768, "32k")):
+            for batch in (1, 8):
+                ms, _, _ = decode_run(batch, long_steps, args.warmup, context, long_runner)
+                points[f"decode_b{batch}_ctx{label}"] = round(batch / (ms / 1e3), 2)
+                bytes_read = weight_bytes + batch * (context + args.warmup + long_steps / 2) * kv_bytes_per_token
+                points[f"decode_b{batch}_ctx{label}_hbm_frac"] = round(bytes_read / (ms / 1e3) / 1e9 / hbm_gbs, 4)
+        del long_runner
+        torch.cuda.empty_cache()
+
+        # end to end through the Python entry point: host ids in, sampled ids out, every step
         e2e_steps = args.steps
         engine = Engine.from_random(
             raw, 0,

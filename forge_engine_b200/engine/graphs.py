@@ -7,8 +7,9 @@ everything eagerly and even synchronises per token (src/forge_engine/engine.py:4
 step is captured once per *bucket* and replayed:
 
 * the bucket fixes the sizes the kernels are launched with: the number of entries (a power
-  of two), the number of tokens (entries for a decode step; else a multiple of 32 up to 256,
-  of 64 beyond), the width of the block tables (a power of two), and what the model's parts
+  of two for a decode step, else as it is), the number of tokens (entries for a decode step;
+  else a multiple of 32 up to 256, of 64 beyond), the width of the block tables (a power of
+  two), and what the model's parts
   decided on the host for this step (``model.plan_step``: for attention, which kernels run and
   with how many splits);
 * the step's integers are copied into the graph's fixed device buffer; filler entries pad the
@@ -106,14 +107,12 @@ class DecodeGraphs:
         if real_tokens == real_entries:                          # one token each: a decode step
             bucket_entries = min(_bucket(real_entries), _bucket(self.max_entries))
             return bucket_entries, bucket_entries, [1] * (bucket_entries - real_entries)
+        # tokens go up to the bucket's count; one filler entry takes all the spare ones (none if
+        # there are none).  The number of entries is not rounded: every entry adds blocks to the
+        # attention kernels' grids, and a step has few.
         bucket_tokens = _token_bucket(real_tokens)
-        bucket_entries = _bucket(real_entries + (1 if bucket_tokens > real_tokens else 0))
-        fillers = bucket_entries - real_entries
-        if fillers > bucket_tokens - real_tokens:                # every filler entry brings a token
-            bucket_tokens = _token_bucket(real_tokens + fillers)
         spare = bucket_tokens - real_tokens
-        counts = [spare - (fillers - 1)] + [1] * (fillers - 1) if fillers else []
-        return bucket_entries, bucket_tokens, counts
+        return real_entries + (1 if spare else 0), bucket_tokens, [spare] if spare else []
 
     def _plan(self, entries, fillers: list, width: int) -> BatchPlan:
         return plan_batch(entries, self.cache, pad_counts=fillers, table_width=width,
@@ -126,7 +125,7 @@ class DecodeGraphs:
         if bucket_tokens == bucket_entries:
             fillers = [1] * bucket_entries
         else:
-            fillers = [bucket_tokens - (bucket_entries - 1)] + [1] * (bucket_entries - 1)
+            fillers = [bucket_tokens - (bucket_entries - 1)] + [1] * (bucket_entries - 1)     # same layout, any split
         plan = self._plan([], fillers, width)
         assert plan.n_tokens == bucket_tokens and plan.n_entries == bucket_entries
         if bucket_tokens != bucket_entries:
