@@ -18,8 +18,15 @@ step is captured once per *bucket* and replayed:
 * every entry is laid out as wanting the logits of its last token, so that the layout does
   not depend on which entries do.
 
-Steps of more than ``MAX_GRAPH_TOKENS`` tokens keep the GPU busy for longer than they take to
-launch and run eagerly, as do steps that want logits elsewhere than at an entry's last token.
+A decode step is captured the first time its bucket is seen.  A bucket of any other step is
+captured only when it has been seen ``capture_after`` times (16): a capture takes two eager
+passes and the capture itself, about 0.1 s at 36 layers, and a replay saves a millisecond
+or two, so shapes that rarely come back are not worth it (64 requests of 16 to 4,096 tokens
+under a budget of 2,048 at the 8B shape: 3.97 s without such captures, 4.4 to 7.2 s when every
+bucket seen twice was captured).  Replay would gain even for a 2,048-token prompt (15.3
+against 16.2 ms at the 4B shape: the gaps between 330 launches), but steps of more than
+``MAX_GRAPH_TOKENS`` tokens (512; FORGE_ENGINE_GRAPH_TOKENS) run eagerly: their shapes vary
+too much.  So do steps that want logits elsewhere than at an entry's last token.
 """
 
 from __future__ import annotations
@@ -29,7 +36,9 @@ import torch
 from ..ops import native
 from .batch import BatchPlan, StepEntry, batch_from_buffer, plan_batch
 
-MAX_GRAPH_TOKENS = 512
+import os
+
+MAX_GRAPH_TOKENS = int(os.environ.get("FORGE_ENGINE_GRAPH_TOKENS", "512"))
 
 
 def _bucket(value: int, floor: int = 1) -> int:
@@ -81,6 +90,8 @@ class DecodeGraphs:
         self.cache = cache
         self.max_entries = max_entries
         self.captured: dict[tuple, _CapturedStep] = {}
+        self.seen: dict[tuple, int] = {}
+        self.capture_after = 16       # sightings of a bucket (other than a decode step's) before it is captured
         self.pool = None
 
     def usable(self) -> bool:
@@ -148,11 +159,13 @@ class DecodeGraphs:
             self.pool = graph.pool()
         return _CapturedStep(graph, buffer, logits, native.LAUNCHES - before)
 
-    def run(self, entries, device_tokens: tuple | None = None) -> torch.Tensor:
+    def run(self, entries, device_tokens: tuple | None = None) -> torch.Tensor | None:
         """Replay the step for ``entries`` (pages already reserved).  Returns logits for the
-        entries that want them, in entry order.  With ``device_tokens = (tensor, rows)`` (steps
-        of one token per entry only) entry i's token is ``tensor[rows[i]]``, copied on the
-        device after the step's other integers have been uploaded."""
+        entries that want them, in entry order - or None when the step's bucket has not been
+        seen often enough to be captured (the caller then launches it eagerly).  With
+        ``device_tokens = (tensor, rows)`` (steps of one token per entry only) entry i's token
+        is ``tensor[rows[i]]``, copied on the device after the step's other integers have been
+        uploaded."""
         bucket_entries, bucket_tokens, fillers = self._shape(entries)
         widest = max(
             (len(self.cache.request(e.key).tables[g].pages) for e in entries for g in range(len(self.cache.groups))),
@@ -171,6 +184,10 @@ class DecodeGraphs:
         full = [StepEntry(e.key, e.tokens, [len(e.tokens) - 1]) for e in entries]
         step = self.captured.get(key)
         if step is None:
+            sightings = self.seen.get(key, 0)
+            self.seen[key] = sightings + 1
+            if bucket_tokens != bucket_entries and sightings < self.capture_after:
+                return None
             step = self._capture(key)
             self.captured[key] = step
         plan = self._plan(full, fillers, width)

@@ -176,10 +176,11 @@ class ModelRunner:
             with torch.cuda.device(self.ctx.device):
                 if device_tokens is not None and not (self.use_graphs and all(len(e.tokens) == 1 for e in entries)):
                     raise ValueError("device tokens need a replayed step of single tokens")
+                logits = None
                 if self.use_graphs and self.graphs.takes(entries):
                     logits = self.graphs.run(entries, device_tokens)
                     n_tokens = sum(len(e.tokens) for e in entries)
-                else:
+                if logits is None:
                     batch = build_batch(entries, self.cache, self.ctx.device)
                     logits = self.model.forward(batch, self.cache)
                     n_tokens = batch.n_tokens

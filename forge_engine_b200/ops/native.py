@@ -8,6 +8,7 @@ a CUDA device or without the library these functions raise ``CUDAUnavailableErro
 from __future__ import annotations
 
 import ctypes
+import os as _os
 from ctypes import c_float, c_int, c_ulonglong, c_void_p
 
 import torch
@@ -481,10 +482,8 @@ def gemm_tc5_set_test_fault(wait_limit: int = 0, skip_kblock: int = -1) -> None:
     fn(int(wait_limit), int(skip_kblock))
 
 
-TC5_MAX_ROWS = 64   # up to this many rows the tcgen05 kernel is used instead of the library GEMM
+TC5_MAX_ROWS = int(_os.environ.get("FORGE_ENGINE_TC5_MAX_ROWS", "64"))   # up to this many rows the tcgen05 kernel is used instead of the library GEMM
 
-
-import os as _os
 
 _ADD_TARGET = int(_os.environ.get("FORGE_ENGINE_ADD_BLOCKS", "288"))
 _ADD_LIMIT = int(_os.environ.get("FORGE_ENGINE_ADD_SPLITS", "16"))
@@ -507,7 +506,7 @@ def tc5_ksplit(o: int, k: int) -> int:
     up to 8 such blocks form a cluster and add their partial tiles through shared memory.
     A block keeps at least four 64-wide k-blocks."""
     tiles = -(-o // 128)
-    return max(1, min(8, round(192 / tiles), (k // 64) // 4))
+    return max(1, min(8, round(int(_os.environ.get("FORGE_ENGINE_TC5_BLOCKS", "192")) / tiles), (k // 64) // 4))
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: torch.Tensor,
