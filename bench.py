@@ -261,6 +261,22 @@ def scheduler_workload(name: str, layers: int | None) -> int:
     seconds = time.perf_counter() - begin
     clocks = sampler.stop()
     made = sum(len(o) for o in outputs)
+    # what a roofline needs: the products' flops over all tokens run (prompt tokens and every
+    # generated token but each request's last, which is never fed back), the attention flops
+    # over the contexts, and the bytes read if every model step streams the weights once and
+    # every decoded token its request's cache
+    hbm_gbs, bf16_tflops, peak_source = peaks()
+    snapshot = engine.scheduler.snapshot()
+    h, q = raw["hidden_size"], raw["num_attention_heads"] * raw["head_dim"]
+    kv, inter = raw["num_key_value_heads"] * raw["head_dim"], raw["intermediate_size"]
+    per_token = 2 * raw["num_hidden_layers"] * (h * (q + 2 * kv) + q * h + 3 * h * inter)
+    tokens_run = snapshot.prefill_tokens + snapshot.decode_tokens
+    attention = sum(4 * raw["num_hidden_layers"] * q * (n + new) * (n + new + 1) // 2 for n in lengths)
+    flops = per_token * tokens_run + attention + 2 * raw["vocab_size"] * h * (made + count)
+    weight_bytes = engine.runner.model.weight_bytes()
+    kv_bytes = engine.runner.cache.bytes_per_token() * sum((n + new // 2) * new for n in lengths)
+    bytes_read = weight_bytes * snapshot.model_steps + kv_bytes
+    sm_mhz = clocks.get("sm_mhz") or 0.0
     print(json.dumps({
         "metric": f"generated tok/s through the scheduler ({name})", "value": round(made / seconds, 1), "unit": "tokens/s",
         "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "impl": "ours",
@@ -272,8 +288,14 @@ def scheduler_workload(name: str, layers: int | None) -> int:
                    "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
                    "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "requests": count,
                    "prompt_min": low, "prompt_max": high, "new_tokens": new, "token_budget": work["token_budget"],
-                   "page_size": PAGE},
+                   "page_size": PAGE, "peaks": peak_source},
         "clocks": clocks,
+        "model_steps": snapshot.model_steps, "prefill_tokens": snapshot.prefill_tokens, "decode_tokens": snapshot.decode_tokens,
+        "roofline": {"flops": flops, "compute_floor_s": round(flops / (bf16_tflops * 1e12), 3),
+                     "bytes": int(bytes_read), "hbm_floor_s": round(bytes_read / (hbm_gbs * 1e9), 3),
+                     "frac": round((flops / (bf16_tflops * 1e12) + bytes_read / (hbm_gbs * 1e9)) / seconds, 4),
+                     "note": "frac = (compute floor + memory floor) / time: prompt steps are bound by flops, decode steps by bytes"},
+        "seconds_x_sm_ghz": round(seconds * sm_mhz / 1e3, 3),
     }))
     return 0
 
