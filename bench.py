@@ -430,6 +430,90 @@ def decode_attention(spec: str) -> int:
     return 0
 
 
+def chain_timeline(tokens: int) -> int:
+    """The output projection, the norm + gate/up projection with SiLU*mul and the down
+    projection of one layer (4B shape, ``tokens`` rows): as the one persistent kernel
+    (``native.decode_chain``) and as the separate kernels the engine launches, 12 layers'
+    worth of distinct weights back to back in a replayed CUDA graph so that the weights come
+    from DRAM; then the persistent kernel's own timeline (nanosecond stamps of every block,
+    taken in one launch in the middle of such a sequence)."""
+    import ctypes
+
+    import torch
+
+    from forge_engine_b200.ops import native
+
+    handle = native.lib()
+    device = "cuda:0"
+    hidden, heads, inter, sets = 2560, 4096, 9728, 12
+
+    def rnd(*shape, scale=0.02):
+        return (torch.randn(*shape, device=device) * scale).bfloat16()
+
+    weights = [dict(o=rnd(hidden, heads), gu=rnd(2 * inter, hidden), d=rnd(hidden, inter)) for _ in range(sets)]
+    norm_w = torch.ones(hidden, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    x = rnd(tokens, heads, scale=1.0)
+    h = torch.randn(tokens, hidden, device=device)
+    act = torch.empty(tokens, inter, dtype=torch.bfloat16, device=device)
+    normed = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device)
+
+    def chain_one(w):
+        native.decode_chain([dict(w=w["o"], x=x, out=h, src=native.CHAIN_SRC_ACTIVATIONS, epi=native.CHAIN_ADD),
+                             dict(w=w["gu"], x=h, norm_w=norm_w, eps=1e-6, out=act, src=native.CHAIN_SRC_NORM,
+                                  epi=native.CHAIN_SILU_MUL),
+                             dict(w=w["d"], x=act, out=h, src=native.CHAIN_SRC_ACTIVATIONS, epi=native.CHAIN_ADD)],
+                            tokens, status)
+
+    def separate_one(w):
+        native.gemm_tc5(x, w["o"], h, native.TC5_ADD_F32, status, ksplit=native.tc5_ksplit_add(hidden, heads))
+        native.add_rmsnorm(h, None, norm_w, normed, 1e-6)
+        native.gemm_tc5(normed, w["gu"], act, native.TC5_SILU_MUL, status, ksplit=native.tc5_ksplit(2 * inter, hidden))
+        native.gemm_tc5(act, w["d"], h, native.TC5_ADD_F32, status, ksplit=native.tc5_ksplit_add(hidden, inter))
+
+    result = {"metric": "o-projection + norm + gate/up + down of one layer, 4B shape", "tokens": tokens, "impl": "ours",
+              "bytes": (hidden * heads + 3 * inter * hidden) * 2}
+    for name, one in (("chain_us", chain_one), ("separate_us", separate_one)):
+        for w in weights:
+            one(w)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for w in weights:
+                one(w)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(10):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        result[name] = round(begin.elapsed_time(end) * 1e3 / 10 / sets, 2)
+    handle.fe_decode_chain_blocks.restype = ctypes.c_int
+    blocks = handle.fe_decode_chain_blocks()
+    trace = torch.zeros(blocks * 16, dtype=torch.int64, device=device)
+    for w in weights[:6]:
+        chain_one(w)
+    handle.fe_decode_chain_trace.argtypes = [ctypes.c_void_p]
+    handle.fe_decode_chain_trace(trace.data_ptr())
+    chain_one(weights[6])
+    handle.fe_decode_chain_trace(None)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    stamps = trace.view(blocks, 16).cpu().double()
+    origin = stamps[:, 0].min()
+    names = ["block starts"] + [f"projection {j}: {what}" for j in range(3)
+                                for what in ("input complete", "token tiles in shared memory", "last product issued",
+                                             "share published", "last weight tile requested")]
+    print(json.dumps(result))
+    for index, name in enumerate(names):
+        column = (stamps[:, index] - origin) / 1e3
+        print(f"# {name:48s} min {column.min():7.2f}  median {column.median():7.2f}  max {column.max():7.2f} us")
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -448,6 +532,12 @@ def main() -> int:
                         help="instead: decode attention alone at these context lengths, split and balanced kernel")
     parser.add_argument("--kernels", action="store_true",
                         help="instead: this repository's kernels at the three kernel shapes upstream publishes")
+    parser.add_argument("--chain-timeline", type=int, metavar="TOKENS",
+                        help="instead: the persistent kernel for a layer's last three projections against the "
+                             "separate kernels, and its per-block timeline")
+    parser.add_argument("--step-timeline", action="store_true",
+                        help="also print, per kernel of one replayed decode step, the time from the end of the kernel "
+                             "before it to its own end (for profiles/)")
     parser.add_argument("--kernel-times", action="store_true",
                         help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()
@@ -468,6 +558,8 @@ def main() -> int:
         return kernel_shapes()
     if args.decode_attention:
         return decode_attention(args.decode_attention)
+    if args.chain_timeline:
+        return chain_timeline(args.chain_timeline)
 
     import torch
 
@@ -610,6 +702,32 @@ def main() -> int:
         for name, (count, total) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
             print(f"# {total:9.1f} us {100 * total / whole:5.1f}%  x{count:<4d} {total / count:7.1f} us each  {name[:90]}")
 
+    def step_timeline(step) -> None:
+        """Kernels of a replayed step overlap (programmatic dependent launch), so a kernel's own
+        duration says little; the time from the end of the kernel before it to its own end adds
+        up to the step.  CUPTI through torch.profiler: shares for reading, never a bench value."""
+        from torch.profiler import ProfilerActivity, profile
+
+        step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        events = [e for e in prof.events()
+                  if e.device_type == torch.autograd.DeviceType.CUDA and "emcpy" not in e.name and "emset" not in e.name]
+        events.sort(key=lambda e: e.time_range.end)
+        previous = events[0].time_range.start
+        rows: dict = {}
+        for event in events:
+            name = event.name.replace("(anonymous namespace)::", "").replace("void ", "")[:70]
+            count, total = rows.get(name, (0, 0.0))
+            rows[name] = (count + 1, total + event.time_range.end - previous)
+            previous = event.time_range.end
+        whole = sum(total for _, total in rows.values())
+        print(f"# end-to-end shares of one step: {whole:.0f} us over {len(events)} kernels, {whole / layers:.1f} us per layer")
+        for name, (count, total) in rows.items():
+            print(f"# {total:9.1f} us {100 * total / whole:5.1f}%  x{count:<4d} {total / count:7.2f} us each  {name}")
+
     if args.prefill_only:
         record = {"prefill": prefill_run(max(1, args.steps)), "layers": layers, "impl": "ours"}
         if args.kernel_times:
@@ -632,6 +750,15 @@ def main() -> int:
             runner.cache.reserve(key, CONTEXT)
             runner.cache.advance(key, CONTEXT)
         kernel_times(lambda: runner.step([StepEntry(k, [7], [0]) for k in keys]))
+        for key in keys:
+            runner.end(key)
+    if args.step_timeline:
+        keys = [f"tl{i}" for i in range(args.batch)]
+        for key in keys:
+            runner.begin(key)
+            runner.cache.reserve(key, CONTEXT)
+            runner.cache.advance(key, CONTEXT)
+        step_timeline(lambda: runner.step([StepEntry(k, [7], [0]) for k in keys]))
         for key in keys:
             runner.end(key)
     value = args.batch / (ms_step / 1e3)
