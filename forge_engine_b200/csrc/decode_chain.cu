@@ -51,7 +51,6 @@ constexpr int CH_A_BYTES = BM * BK * 2;         // 16 KB weight tile
 constexpr int CH_B_TILE = CH_BN * BK * 2;       // 2 KB token tile of one k-block
 constexpr int CH_B_TILES = 44;                  // token tiles a block keeps for one projection
 constexpr int CH_NORM_PIECES = CH_B_TILES * 8 / 32;   // 16-byte pieces of a normalised row per lane
-constexpr int CH_AHEAD = 16;                   // weight tiles asked into L2 beyond the ring
 constexpr int CH_MAX_OPS = 3;
 constexpr int CH_MAX_LEFT = 160;                // leftover tiles of one projection (fewer than blocks)
 constexpr int CH_COUNTERS = 8 + CH_MAX_OPS * CH_MAX_LEFT;
@@ -179,9 +178,6 @@ __device__ __forceinline__ void cursor_step(TileCursor& c, const ChainParams& p,
   cursor_seek(c, p, blocks, me);
 }
 
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
-}
 __device__ __forceinline__ void red_release_u32(unsigned* p, unsigned v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -248,18 +244,12 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap mw0, const __grid_consta
 
   if (warp == 0) {
     // ---------------- producer: the weights of every unit of every projection, in order.
-    // Beyond the ring it asks for the next CH_AHEAD tiles to be brought into L2: while the
-    // products wait for a hand-over the ring is full and this thread stands still, but
-    // memory keeps streaming, and the ring then refills from L2.
+    // (Asking for tiles beyond the ring to be brought into L2 - cp.async.bulk.prefetch.tensor,
+    // 16 tiles ahead - kept memory busy while the products waited for a hand-over, but slowed
+    // the stream itself, gate/up from 14.6 to 19.2 us, and read 20 % more from DRAM: taken out.)
     if (lane == 0) {
-      TileCursor load = {0, 0, 0, 0, 0, 0, false}, ahead = {0, 0, 0, 0, 0, 0, false};
+      TileCursor load = {0, 0, 0, 0, 0, 0, false};
       cursor_seek(load, p, blocks, me);
-      ahead = load;
-      for (int i = 0; i < CH_STAGES && ahead.valid; ++i) cursor_step(ahead, p, blocks, me);
-      for (int i = 0; i < CH_AHEAD && ahead.valid; ++i) {
-        tma_prefetch_2d(pick(ahead.j, &mw0, &mw1, &mw2), ahead.kb * BK, ahead.tile * BM);
-        cursor_step(ahead, p, blocks, me);
-      }
       unsigned it = 0;
       int last_j = 0;
       while (load.valid) {
@@ -273,10 +263,6 @@ decode_chain_kernel(const __grid_constant__ CUtensorMap mw0, const __grid_consta
         tma_load_2d(a_tiles + s * CH_A_BYTES, pick(load.j, &mw0, &mw1, &mw2), load.kb * BK, load.tile * BM, full + s);
         cursor_step(load, p, blocks, me);
         ++it;
-        if (ahead.valid) {
-          tma_prefetch_2d(pick(ahead.j, &mw0, &mw1, &mw2), ahead.kb * BK, ahead.tile * BM);
-          cursor_step(ahead, p, blocks, me);
-        }
       }
       CH_STAMP(1 + 5 * last_j + 4);
     }
