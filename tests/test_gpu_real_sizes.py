@@ -299,3 +299,31 @@ def test_full_depth_and_vocabulary() -> None:
         top = torch.topk(ref, 2, dim=-1).values
         clear = (top[:, 0] - top[:, 1]) > 2 * BF16_REL * max(1.0, float(ref.abs().max()))
         assert torch.equal(got.argmax(-1)[clear], ref.argmax(-1)[clear]), name
+
+
+def test_decode_steps_through_the_persistent_chain_kernel(two_layers, monkeypatch) -> None:
+    """FORGE_ENGINE_DECODE_CHAIN=1: a layer's output projection, post-attention norm, gate/up
+    with SiLU*mul and down projection run as one persistent kernel for steps of up to 16
+    tokens (off by default: it measured slower than the separate kernels).  Three requests
+    decode together after prompts of different lengths, replayed from a graph, against the
+    plain implementation."""
+    from forge_engine_b200.engine import StepEntry
+    from forge_engine_b200.ops import native
+
+    monkeypatch.setenv("FORGE_ENGINE_DECODE_CHAIN", "1")
+    launches = []
+    real = native.decode_chain
+    monkeypatch.setattr(native, "decode_chain", lambda ops, n, status: (launches.append(n), real(ops, n, status))[1])
+    lengths = (70, 9, 33)
+    sequences = [random_ids(5003, n + 6, 700 + n) for n in lengths]
+    expected = [two_layers.plain_logits(s)[-6:] for s in sequences]
+    runner = two_layers.runner("bfloat16", pages=24, requests=3)
+    for i, (n, ids) in enumerate(zip(lengths, sequences)):
+        runner.begin(i)
+        runner.step([StepEntry(i, ids[:n], [])])
+    assert launches == [9, 9]                     # only the 9-token prompt is short enough; two layers
+    rows = [runner.step([StepEntry(i, [sequences[i][lengths[i] + t]], [0]) for i in range(3)]).cpu() for t in range(6)]
+    runner.check_status()
+    assert launches[2:] == [4] * 6                # captured once: two warm-up passes and the capture, bucket of 4
+    for i in range(3):
+        check_rows("bfloat16", torch.stack([rows[t][i] for t in range(6)]), expected[i], f"request {i}")
