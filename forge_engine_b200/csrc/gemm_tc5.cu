@@ -73,11 +73,14 @@ struct GemmParams {
   QkvRope rope;          // EPI_QKV_ROPE only
 };
 
-template <int BN> __host__ __device__ constexpr int stages_for() {
+template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
   // stage = weight tile (16 KB) + token tile (BN * 128 B).  Narrow token tiles keep the ring
   // at about 100 KB (108, 100 and 96 KB for 16, 32 and 64 tokens), two blocks per SM, so that
   // one block's epilogue and set-up overlap another's streaming and a product's 150-190
   // blocks all run at once; the widest tile takes the SM alone.
+  // (The gate/up product has about one block per SM; eight stages and the SM to itself for its
+  // 64-token form measured worse, 6.44 against 5.81 ms per step at batch 64: the next product's
+  // blocks then find no room to become resident and fill their rings meanwhile.)
   return BN <= 16 ? 6 : (BN <= 32 ? 5 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4)));
 }
 
@@ -192,7 +195,7 @@ __device__ __forceinline__ void store_one(const GemmParams& p, float v, int feat
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
-  constexpr int STAGES = stages_for<BN>();
+  constexpr int STAGES = stages_for<BN, EPI>();
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static_assert(BN > CLUSTER_REDUCE_TOKENS || BN * BM * 4 <= STAGES * (A_BYTES + B_BYTES),
@@ -505,8 +508,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, FE_STATUS_WAIT_TIMEOUT);
 }
 
-template <int BN> constexpr size_t smem_bytes() {
-  return (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + (2 * stages_for<BN>() + 1) * 8 + 16 + 2 * 136 * 4 + 1024;
+template <int BN, int EPI> constexpr size_t smem_bytes() {
+  return (size_t)stages_for<BN, EPI>() * (BM * BK * 2 + BN * BK * 2) + (2 * stages_for<BN, EPI>() + 1) * 8 + 16 + 2 * 136 * 4 + 1024;
 }
 
 template <int BN, int EPI>
@@ -514,11 +517,11 @@ int launch_one(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p
   static bool configured = false;
   if (!configured) {
     const cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)smem_bytes<BN>());
+                                               (int)smem_bytes<BN, EPI>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int rc = fe_launch_dependent_cluster(gemm_tc5_kernel<BN, EPI>, grid, dim3(THREADS), smem_bytes<BN>(), stream,
+  const int rc = fe_launch_dependent_cluster(gemm_tc5_kernel<BN, EPI>, grid, dim3(THREADS), smem_bytes<BN, EPI>(), stream,
                                              p.cluster_reduce ? p.ksplit : 1, mw, mx, p);
   if (rc) return rc;
   return fe_last_error();
