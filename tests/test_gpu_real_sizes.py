@@ -327,3 +327,36 @@ def test_decode_steps_through_the_persistent_chain_kernel(two_layers, monkeypatc
     assert launches[2:] == [4] * 6                # captured once: two warm-up passes and the capture, bucket of 4
     for i in range(3):
         check_rows("bfloat16", torch.stack([rows[t][i] for t in range(6)]), expected[i], f"request {i}")
+
+
+@pytest.mark.parametrize("dtype,length", [("float32", 3000), ("bfloat16", 6000)])
+def test_long_context_in_portions_then_decoding(two_layers, dtype, length) -> None:
+    """A prompt of several thousand tokens fed in portions of 2,048 (block tables hundreds of
+    pages wide, prefill portions that start thousands of tokens into the request), then
+    decoded tokens whose attention is split 16 to 32 ways; beside it a short request, so that
+    the decode steps hold very uneven contexts.  Logits at the ends of the portions and of
+    every decoded token against the plain implementation."""
+    from forge_engine_b200.engine import StepEntry
+
+    long_ids = random_ids(5003, length + 5, 41)
+    short_ids = random_ids(5003, 40 + 5, 42)
+    ref_long, ref_short = two_layers.plain_logits(long_ids), two_layers.plain_logits(short_ids)
+    runner = two_layers.runner(dtype, pages=-(-(length + 5) // 16) + 8, requests=2)
+    runner.begin("long"), runner.begin("short")
+    fed, rows, wanted = 0, [], []
+    while fed < length:
+        n = min(2048, length - fed)
+        rows.append(runner.step([StepEntry("long", long_ids[fed : fed + n], [0, n - 1])]).cpu())
+        wanted += [fed, fed + n - 1]
+        fed += n
+    check_rows(dtype, torch.cat(rows), ref_long[wanted], "ends of the long prompt's portions")
+    out = runner.step([StepEntry("short", short_ids[:40], [39])]).cpu()
+    check_rows(dtype, out, ref_short[39:40], "short prompt")
+    for t in range(5):
+        out = runner.step([StepEntry("long", [long_ids[length + t]], [0]),
+                           StepEntry("short", [short_ids[40 + t]], [0])]).cpu()
+        check_rows(dtype, out[0:1], ref_long[length + t : length + t + 1], f"long request, decoded token {t}")
+        check_rows(dtype, out[1:2], ref_short[40 + t : 41 + t], f"short request, decoded token {t}")
+    runner.check_status()
+    if dtype == "bfloat16":
+        assert any(key[2] >= 256 for key in runner.graphs.captured)       # block tables of 376 pages: bucket 512
