@@ -523,6 +523,9 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--shape", default="4b", choices=("4b", "8b", "32b"),
+                        help="layer sizes of the decode benchmark: the 4B shape of the headline, or the 8B / 32B "
+                             "shapes of the workloads (use --layers to keep it short)")
     parser.add_argument("--skip-points", action="store_true", help="skip batch 1/64, prefill and e2e")
     parser.add_argument("--prefill-only", action="store_true",
                         help="time only the 2,048-token prefill (small cases for profiling)")
@@ -568,6 +571,8 @@ def main() -> int:
     from forge_engine_b200.ops import native
 
     raw = dict(CONFIG_4B)
+    if args.shape != "4b":
+        raw = dict(WORKLOADS["mixed-8b" if args.shape == "8b" else "long-32b"]["config"])
     layers_full = raw["num_hidden_layers"]
     if args.layers:
         raw["num_hidden_layers"] = args.layers
@@ -765,7 +770,7 @@ def main() -> int:
     step_bytes = weight_bytes + args.batch * (CONTEXT + args.warmup + args.steps / 2) * kv_bytes_per_token
     achieved = step_bytes / (ms_step / 1e3) / 1e9
     record = {
-        "metric": "decode tok/s (Qwen3-4B shape, bf16, batch 8, 2048-token contexts)",
+        "metric": f"decode tok/s (Qwen3-{args.shape.upper()} shape, bf16, batch {args.batch}, 2048-token contexts)",
         "value": round(value, 2),
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -779,7 +784,7 @@ def main() -> int:
         "data": "synthetic token ids (seed 5), random weights (seed 0), contexts are random cache pages",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-4B shape",
+            "model": f"Qwen3-{args.shape.upper()} shape",
             "layers": layers,
             "layers_full": layers_full,
             "hidden": raw["hidden_size"],
@@ -792,7 +797,7 @@ def main() -> int:
             "seq_len": CONTEXT,
             "max_context": raw["max_position_embeddings"],
             "page_size": PAGE,
-            "tied_embeddings": True,
+            "tied_embeddings": bool(raw["tie_word_embeddings"]),
             "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights %.1f GB read every step)" % (weight_bytes / 1e9),
             "peaks": peak_source,
