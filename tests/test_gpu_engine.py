@@ -1004,6 +1004,36 @@ def test_mixed_steps_replayed_from_graphs_equal_eager_steps(fe, dtype, name, tmp
                 assert torch.equal(eager, replayed)
 
 
+def test_scheduler_run_with_buckets_captured_midway_gives_the_eager_tokens(fe, tmp_path) -> None:
+    """A long scheduler run under a small token budget with the default capture policy: the
+    buckets of its mixed steps are seen 16 times, captured in the middle of the run and
+    replayed from then on.  Configuration D has two windowed layers (pages are given back
+    while requests live).  Every request's greedy tokens equal those of the same run launched
+    eagerly, and the plain implementation's."""
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine, ModelRunner
+    from forge_engine_b200.sampling import SamplingParams
+
+    cfg, weights = make_model_folder(tmp_path / "m", dict(plain.TINY_D, eos_token_id=None), 6)
+    prompts = [random_ids(cfg.vocab_size, 40, 800 + i) for i in range(40)]
+    sched = SchedulerConfig(max_requests=40, max_batch_size=4, token_budget=12, chunk_size=8, block_size=4,
+                            block_capacity=200, lookahead=False)
+    outputs = {}
+    for graphs in (False, True):
+        runner = ModelRunner.from_folder(tmp_path / "m", dtype="float32", page_size=4, num_pages=200, max_requests=40,
+                                         use_graphs=graphs)
+        engine = Engine(runner, EngineConfig(max_new_tokens=5, dtype="float32"), sched)
+        outputs[graphs] = engine.generate(prompts, SamplingParams(max_new_tokens=5))
+        if graphs:
+            assert runner.graphs.capture_after == 16
+            mixed = [key for key in runner.graphs.captured if key[0] != key[1]]
+            assert mixed, sorted(runner.graphs.seen.items(), key=lambda kv: -kv[1])[:5]
+        assert all(n == 0 for n in runner.cache.leased_pages())
+    assert outputs[True] == outputs[False]
+    for prompt, output in list(zip(prompts, outputs[True]))[:6]:
+        assert output == plain.greedy_generate(prompt, 5, weights, cfg)
+
+
 def test_lookahead_gives_the_same_tokens_as_synchronous_steps(fe, tmp_path) -> None:
     """Decode steps launched one ahead (tokens fed on the device, events one step late)
     against fully synchronous scheduling: same outputs, greedy and sampled, with requests
