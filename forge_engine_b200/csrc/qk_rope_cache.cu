@@ -197,6 +197,104 @@ __global__ void qk_rope_cache_vec_kernel(bf16* __restrict__ qkv, const float* __
   }
 }
 
+// The same for a projection whose k-splits met in a 32-bit buffer through atomic adds
+// (`sums` [n, (nq + 2 nkv) * D], bias already added): reads the sums, puts zeros back - the
+// buffer is then ready for the next projection that adds into it -, norms and rotates in
+// 32-bit and stores q as bfloat16 into `q_out` (same row layout; only the q columns are
+// written) and k, v into their pages.  Same arithmetic as above, on the unrounded sums.
+template <int D>
+__global__ void qk_rope_cache_sums_kernel(float* __restrict__ sums, bf16* __restrict__ q_out,
+                                          const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                          float eps, const float* __restrict__ inv_freq,
+                                          const float2* __restrict__ table, const int* __restrict__ positions,
+                                          const int* __restrict__ token_entry, PagedKV cache, int num_q_heads,
+                                          int write_kv, int* status) {
+  constexpr int LANES = D / 8;
+  constexpr int HEADS = 32 / LANES;
+  constexpr int HALF = D / 2;
+  pdl_trigger();
+  const int token = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LANES, l = lane - sub * LANES;
+  const int warps = (blockDim.x >> 5) * gridDim.y;
+  const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int nkv = cache.num_kv_heads;
+  const int heads_total = num_q_heads + 2 * nkv;
+  // the step's own integers and the rotation table do not depend on the projection
+  const int pos = positions[token];
+  const int entry = token_entry[token];
+  int page = -1, slot = 0;
+  if (write_kv) {
+    const int logical = pos / cache.page_size;
+    slot = pos - logical * cache.page_size;
+    if (pos < 0 || logical >= cache.max_pages) {
+      if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, FE_STATUS_BAD_POSITION);
+    } else {
+      page = cache.block_table[(size_t)entry * cache.max_pages + logical];
+      if (page < 0 || page >= cache.num_pages) {
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, FE_STATUS_BAD_PAGE);
+        page = -1;
+      }
+    }
+  }
+  const int j0 = 4 * l;
+  pdl_wait();
+  float cs[4], sn[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    cs[e] = 1.f; sn[e] = 0.f;
+    if (table) {
+      const float2 both = table[(size_t)token * HALF + j0 + e];
+      cs[e] = both.x;
+      sn[e] = both.y;
+    } else if (inv_freq) {
+      const float angle = (float)pos * inv_freq[j0 + e];
+      cs[e] = cosf(angle);
+      sn[e] = sinf(angle);
+    }
+  }
+  unsigned group_mask = 0xffffffffu;
+  if constexpr (LANES < 32) group_mask = ((1u << LANES) - 1u) << (sub * LANES);
+  const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int head = warp * HEADS + sub; head < heads_total; head += warps * HEADS) {
+    float* x = sums + (size_t)token * heads_total * D + (size_t)head * D;
+    const bool is_q = head < num_q_heads;
+    const bool is_k = !is_q && head < num_q_heads + nkv;
+    float a[4], b[4];
+    load4(x + j0, a);
+    load4(x + HALF + j0, b);
+    store4(x + j0, zero);
+    store4(x + HALF + j0, zero);
+    if (!is_q && (!write_kv || page < 0)) continue;
+    bf16* dst = q_out + (size_t)token * heads_total * D + (size_t)head * D;
+    if (!is_q) {
+      const int kvh = is_k ? head - num_q_heads : head - num_q_heads - nkv;
+      dst = (bf16*)(is_k ? cache.k : cache.v) + kv_offset(cache, page, kvh, slot);
+    }
+    if (is_q || is_k) {
+      const float* w = is_q ? q_weight : k_weight;
+      float inv = 1.f;
+      if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+#pragma unroll
+        for (int offset = LANES / 2; offset > 0; offset >>= 1) ss += __shfl_xor_sync(group_mask, ss, offset);
+        inv = rsqrtf(ss / (float)D + eps);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float u = a[e] * inv, v = b[e] * inv;
+        if (w) { u *= w[j0 + e]; v *= w[j0 + e + HALF]; }
+        a[e] = u * cs[e] - v * sn[e];
+        b[e] = v * cs[e] + u * sn[e];
+      }
+    }
+    store4(dst + j0, a);
+    store4(dst + HALF + j0, b);
+  }
+}
+
 // cos and sin of float(position) * inv_freq[j] for every token and pair j, taken once per
 // step: table [n, half] of (cos, sin).  The angles are the same in every layer.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half, int n,
@@ -266,4 +364,32 @@ FE_EXPORT int fe_qk_rope_cache(void* qkv, int dtype, const float* q_weight, cons
   else
     return FE_ERR_BAD_DTYPE;
   return fe_last_error();
+}
+
+// The form for 32-bit sums of a projection's atomic k-splits (see qk_rope_cache_sums_kernel):
+// head sizes 64, 128 and 256, the whole head rotated (or no rotation: inv_freq and table null).
+FE_EXPORT int fe_qk_rope_cache_sums(float* sums, void* q_out, const float* q_weight, const float* k_weight, float eps,
+                                    const float* inv_freq, const void* table, const int* positions,
+                                    const int* token_entry, void* k_cache, void* v_cache, const int* block_table,
+                                    int max_pages, int page_size, int num_pages, int num_q_heads, int num_kv_heads,
+                                    int head_dim, int n_tokens, int write_kv, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return FE_ERR_BAD_SHAPE;
+  if ((((uintptr_t)sums) & 15) || (((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 7)) return FE_ERR_BAD_ALIGN;
+  PagedKV cache{k_cache, v_cache, block_table, max_pages, page_size, num_pages, num_kv_heads, head_dim};
+  const int heads_total = num_q_heads + 2 * num_kv_heads;
+  const int at_a_time = 256 / head_dim;
+  const int slots = (heads_total + at_a_time - 1) / at_a_time;
+  const int per_warp = n_tokens >= 512 ? 4 : 1;
+  const int need = (slots + per_warp - 1) / per_warp;
+  const int w = need < 4 ? need : 4;
+  dim3 grid(n_tokens, (need + w - 1) / w);
+#define LAUNCH_SUMS(DIM)                                                                                          \
+  return fe_launch_dependent(qk_rope_cache_sums_kernel<DIM>, grid, dim3(w * 32), 0, stream, sums, (bf16*)q_out, q_weight, \
+                             k_weight, eps, inv_freq, (const float2*)table, positions, token_entry, cache, num_q_heads,    \
+                             write_kv, status)
+  if (head_dim == 64) LAUNCH_SUMS(64);
+  if (head_dim == 128) LAUNCH_SUMS(128);
+  LAUNCH_SUMS(256);
+#undef LAUNCH_SUMS
 }

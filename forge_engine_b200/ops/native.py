@@ -60,6 +60,7 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_add_rmsnorm": [p, p, i, p, p, i, p, i, i, f, i, p],
         "fe_silu_mul": [p, p, i, i, i, i, p],
         "fe_qk_rope_cache": [p, i, p, p, f, p, p, i, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
+        "fe_qk_rope_cache_sums": [p, p, p, p, f, p, p, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
         "fe_rope_table": [p, p, i, i, p, p],
         "fe_attention_simt": [p, i, i, p, p, p, i, i, i, p, p, i, f, p, i, i, i, i, p, p],
         "fe_gemm_simt": [p, i, p, i, p, p, i, i, i, i, i, p],
@@ -327,6 +328,56 @@ def qk_rope_cache(
         ),
         "qk_rope_cache",
     )
+
+
+def qk_rope_cache_sums(
+    sums: torch.Tensor,
+    q_out: torch.Tensor,
+    q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None,
+    eps: float,
+    inv_freq: torch.Tensor | None,
+    positions: torch.Tensor,
+    token_entry: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    num_q_heads: int,
+    write_kv: bool,
+    status: torch.Tensor,
+    table: torch.Tensor | None = None,
+) -> None:
+    """``qk_rope_cache`` for a projection whose k-splits were added into the 32-bit ``sums``
+    [N, (nq + 2 nkv) * D]: reads the sums and leaves zeros behind, stores the finished
+    queries as bfloat16 into the q columns of ``q_out`` (same shape) and k, v into their
+    bfloat16 pages.  The whole head is rotated (or none of it: inv_freq and table None)."""
+    _dense(sums, "sums"), _dense(q_out, "q_out"), _dense(k_cache, "k_cache"), _dense(v_cache, "v_cache")
+    _dense(block_table, "block_table")
+    num_pages, nkv, page_size, head_dim = k_cache.shape
+    n = q_out.shape[0]
+    width = (num_q_heads + 2 * nkv) * head_dim
+    assert sums.dtype == torch.float32 and sums.numel() >= n * width and q_out.shape == (n, width)
+    assert q_out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2
+    assert positions.dtype == torch.int32 and token_entry.dtype == torch.int32
+    for w in (q_weight, k_weight, inv_freq, table):
+        assert w is None or (w.dtype == torch.float32 and w.is_cuda and w.is_contiguous())
+    assert table is None or table.shape == (n, head_dim // 2, 2)
+    check(
+        lib().fe_qk_rope_cache_sums(
+            ptr(sums), ptr(q_out), ptr(q_weight), ptr(k_weight), float(eps), ptr(inv_freq), ptr(table),
+            ptr(positions), ptr(token_entry), ptr(k_cache), ptr(v_cache), ptr(block_table),
+            block_table.shape[1], page_size, num_pages, num_q_heads, nkv, head_dim, n,
+            1 if write_kv else 0, ptr(status), stream(),
+        ),
+        "qk_rope_cache_sums",
+    )
+
+
+def projection_sums(device: torch.device, count: int) -> torch.Tensor:
+    """A 32-bit buffer of at least ``count`` zeros that lives as long as the process, for
+    projections that add their k-splits into it; whoever reads the sums puts zeros back."""
+    return _scratch.get("projection sums", device, count, torch.float32, 1 << 20, zero=True)
 
 
 def attention_simt(

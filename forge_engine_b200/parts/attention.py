@@ -227,7 +227,20 @@ class GQAttention(Mixer):
         k_cache, v_cache = cache.kv
         table = batch.group_tables[cache.group]
         rotary = self.position.rotary()
-        if self._fused_projection(x, rotary, k_cache):
+        if self._summed_projection(x, rotary, k_cache):
+            # few tokens: the projection's k-splits add into a zeroed 32-bit buffer (no cluster,
+            # more blocks), and the norm-and-rotate kernel reads the sums and leaves zeros behind
+            width = self.qkv_proj.out_features
+            sums = native.projection_sums(x.device, x.shape[0] * width)[: x.shape[0] * width].view(x.shape[0], width)
+            native.gemm_tc5(x, self.qkv_proj.weight, sums, native.TC5_ADD_F32, self.ctx.status, bias=self.qkv_proj.bias,
+                            ksplit=native.tc5_ksplit_add(width, self.qkv_proj.in_features))
+            qkv = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+            native.qk_rope_cache_sums(
+                sums, qkv, self.q_norm, self.k_norm, self.spec.qk_norm_eps, None if rotary is None else rotary[0],
+                batch.positions, batch.token_entry, k_cache, v_cache, table, self.nq, cache.owns, self.ctx.status,
+                table=self.position.table(batch) if rotary is not None and hasattr(self.position, "table") else None,
+            )
+        elif self._fused_projection(x, rotary, k_cache):
             # few tokens, heads of 128: norm, rotation and the page write happen in the
             # projection's own epilogue
             qkv = torch.empty((x.shape[0], self.qkv_proj.out_features), dtype=x.dtype, device=x.device)
@@ -253,6 +266,18 @@ class GQAttention(Mixer):
                 cache.owns, self.ctx.status, table=angles,
             )
         return qkv
+
+    def _summed_projection(self, x, rotary, k_cache) -> bool:
+        """Whether the q/k/v projection adds its k-splits into a 32-bit buffer that a separate
+        norm-and-rotate kernel reads: few tokens, the tcgen05 kernel takes the call, and the
+        position encoding rotates whole heads.  Up to FORGE_ENGINE_SUMMED_QKV tokens (64; 0 turns
+        it off).  Measured at the 4B shape against the projection that sums its k-splits inside
+        a cluster and norms and rotates in its own epilogue: 2.473 against 2.509 ms a decode
+        step at batch 8, 2.940 against 3.017 at 16, 3.866 against 3.921 at 32, 5.82 against 5.85
+        at 64, no difference at batch 1 and 2."""
+        limit = int(os.environ.get("FORGE_ENGINE_SUMMED_QKV", "64"))
+        return (x.shape[0] <= limit and self.d in (64, 128, 256) and rotary is not None and rotary[1] == self.d
+                and k_cache.dtype == torch.bfloat16 and self.qkv_proj._tc5_ok(x))
 
     def _fused_projection(self, x, rotary, k_cache) -> bool:
         """Whether the q/k/v projection's epilogue can do the per-head norms, the rotation

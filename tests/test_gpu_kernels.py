@@ -305,6 +305,67 @@ def test_qk_rope_cache(native, dtype, nq, nkv, d, rot, norm) -> None:
     assert int(status.item()) & 4
 
 
+@pytest.mark.parametrize("nq,nkv,d,norm,with_table,write", [(32, 8, 128, True, True, True), (6, 2, 64, True, False, True),
+                                                            (3, 1, 256, True, True, True), (5, 1, 128, False, True, True),
+                                                            (7, 3, 64, True, True, False)])
+def test_qk_rope_cache_from_sums(native, nq, nkv, d, norm, with_table, write) -> None:
+    """The form that reads 32-bit sums (where a projection's k-splits were added) and leaves
+    zeros behind: queries as bfloat16 into the q columns of another buffer, k and v into
+    their pages, against the plain norm and rotation of the same 32-bit numbers."""
+    g = torch.Generator().manual_seed(d + nq)
+    page, theta, eps = 8, 54321.0, 3e-6
+    table = torch.tensor([[4, 1, 6, -1], [0, 5, -1, -1]], dtype=torch.int32, device=DEV)
+    positions = list(range(13, 21)) + list(range(0, 9))
+    entry = [0] * 8 + [1] * 9
+    n = len(positions)
+    width = (nq + 2 * nkv) * d
+    x = torch.randn((n, width), generator=g)
+    qw, kw = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    k_cache = torch.zeros((7, nkv, page, d), dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    dev_positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    angles = None
+    if with_table:
+        angles = torch.empty((n, d // 2, 2), dtype=torch.float32, device=DEV)
+        native.rope_table(dev_positions, inv_freq.to(DEV), angles)
+    sums = native.projection_sums(torch.device(DEV), n * width)
+    assert float(sums.abs().max()) == 0          # zero when handed out, and after every use
+    view = sums[: n * width].view(n, width)
+    view.copy_(x)
+    out = torch.full((n, width), 7.0, dtype=torch.bfloat16, device=DEV)
+    status = status_word()
+    native.qk_rope_cache_sums(view, out, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, eps, inv_freq.to(DEV),
+                              dev_positions, torch.tensor(entry, dtype=torch.int32, device=DEV), k_cache, v_cache, table,
+                              nq, write, status, table=angles)
+    assert int(status.item()) == 0
+    assert float(sums.abs().max()) == 0
+    q = x[:, : nq * d].view(n, nq, d)
+    k = x[:, nq * d : (nq + nkv) * d].view(n, nkv, d)
+    v = x[:, (nq + nkv) * d :].view(n, nkv, d)
+    if norm:
+        q, k = plain.rms_norm(q, qw, eps), plain.rms_norm(k, kw, eps)
+    cosine, sine = plain.rotary_tables(torch.tensor(positions), d, theta, torch.float32)
+    rotate = lambda t: plain.apply_rotary(t.transpose(0, 1), cosine, sine).transpose(0, 1)   # noqa: E731
+    bound = dict(atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(out[:, : nq * d].float().cpu().view(n, nq, d), rotate(q), **bound)
+    assert float((out[:, nq * d :].float() - 7.0).abs().max()) == 0      # the k and v columns are not written
+    if not write:
+        assert float(k_cache.abs().sum()) == 0 and float(v_cache.abs().sum()) == 0
+        return
+    k_ref = rotate(k)
+    for i, (e, p) in enumerate(zip(entry, positions)):
+        page_id = int(table[e, p // page])
+        torch.testing.assert_close(k_cache[page_id, :, p % page].float().cpu(), k_ref[i], **bound)
+        assert torch.equal(v_cache[page_id, :, p % page].cpu(), v[i].to(torch.bfloat16))
+    assert float(k_cache[2].abs().sum()) == 0 and float(k_cache[3].abs().sum()) == 0
+    # a position beyond the table is reported, nothing is written, and the sums are cleared all the same
+    view[:1].fill_(1.0)
+    native.qk_rope_cache_sums(view[:1], out[:1], None, None, eps, None, torch.tensor([40], dtype=torch.int32, device=DEV),
+                              torch.tensor([0], dtype=torch.int32, device=DEV), k_cache, v_cache, table, nq, True, status)
+    assert int(status.item()) & 4 and float(sums.abs().max()) == 0
+
+
 def test_rope_angles_at_large_positions(native) -> None:
     """Angles are float(position) * inv_freq in 32-bit; cos and sin must stay accurate at
     positions in the hundred thousands (no fast-math range reduction)."""

@@ -158,9 +158,8 @@ def test_mixed_trace_with_few_pages(two_layers, dtype) -> None:
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_of_33_64_and_65_tokens(two_layers, dtype, monkeypatch) -> None:
-    """33 and 64 tokens take the 64-token tile of the tcgen05 product (the projection's fused
-    norm/rotation epilogue is off above 16 tokens); 65 tokens are the first that go to the
-    library product.  One request fed 33 + 64 + 65 tokens, a second one beside it in the
+    """33 and 64 tokens take the 64-token tile of the tcgen05 product; 65 tokens are the
+    first that go to the library product.  One request fed 33 + 64 + 65 tokens, a second one beside it in the
     64-token step so that the step is exactly 64 tokens over two entries."""
     from forge_engine_b200.engine import StepEntry
     from forge_engine_b200.ops import native
@@ -184,7 +183,7 @@ def test_steps_of_33_64_and_65_tokens(two_layers, dtype, monkeypatch) -> None:
         # four projections per layer and the output head, all on the tcgen05 kernel ...
         assert own_33 == [33] * 9 and own_64 == [64] * 9
         # ... and none of the 65-token step's (the 9-token step after it is back on it)
-        assert calls[seen:] == [9] * 7
+        assert calls[seen:] == [9] * 9
     else:
         assert not calls
     check_rows(dtype, torch.cat([first, second[:40], third]), ref_a, "request a")
