@@ -204,7 +204,7 @@ __device__ __forceinline__ Tc5Tile tc5_tile(int row0, int rows_total, int start,
   return t;
 }
 
-__global__ void __launch_bounds__(TC5_THREADS)
+__global__ void __launch_bounds__(TC5_THREADS, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -215,13 +215,15 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_tiles + TC5_V_STAGES * TC5_KV_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;                   // [key stages]
-  uint64_t* k_empty = k_full + TC5_K_STAGES;
-  uint64_t* v_full = k_empty + TC5_K_STAGES;     // [value stages]
-  uint64_t* v_empty = v_full + TC5_V_STAGES;
-  uint64_t* s_full = v_empty + TC5_V_STAGES;     // [2 query tiles]
+  uint64_t* v_full = k_full + TC5_K_STAGES;      // [value stages]
+  // freed[n & 3], event n: the tensor core has finished everything issued up to the end of key
+  // tile n - 1 (event 0: the first scores).  Then the stage of value tile n - 1 and the stage of
+  // key tile n may be filled again.  One commit a key tile instead of one per ring: every
+  // commit and every wait is time the issuing thread does not issue in.
+  uint64_t* freed = v_full + TC5_V_STAGES;       // [4]
+  uint64_t* s_full = freed + 4;                  // [2 query tiles]
   uint64_t* p_full = s_full + 2;                 // [2]
-  uint64_t* pv_done = p_full + 2;                // [2] completes once per value product
-  uint64_t* o_full = pv_done + 2;
+  uint64_t* o_full = p_full + 2;
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -253,9 +255,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < TC5_K_STAGES; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
-    for (int s = 0; s < TC5_V_STAGES; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
-    for (int x = 0; x < 2; ++x) { mbar_init(s_full + x, 1); mbar_init(p_full + x, 4); mbar_init(pv_done + x, 1); }
+    for (int s = 0; s < TC5_K_STAGES; ++s) mbar_init(k_full + s, 1);
+    for (int s = 0; s < TC5_V_STAGES; ++s) mbar_init(v_full + s, 1);
+    for (int s = 0; s < 4; ++s) mbar_init(freed + s, 1);
+    for (int x = 0; x < 2; ++x) { mbar_init(s_full + x, 1); mbar_init(p_full + x, 4); }
     mbar_init(o_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -296,9 +299,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         else if (key + p.page_size > key_lo) atomicOr(p.status, FE_STATUS_BAD_PAGE);
       }
       const int offset = lane * p.page_size * 128;
-      // keys
+      // keys; from the third tile on both stages were in use before: key tile i - 2 and value
+      // tile i - 3 are free after event i - 2
       if (lane == 0) {
-        if (i >= TC5_K_STAGES) ok = mbar_wait(k_empty + ks, ((i / TC5_K_STAGES) & 1) ^ 1, abort_flag);
+        if (i >= 2) ok = mbar_wait(freed + ((i - 2) & 3), ((i - 2) >> 2) & 1, abort_flag);
         if (ok) mbar_expect_tx(k_full + ks, TC5_KV_BYTES);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -309,12 +313,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tma_load_2d(k_tiles + ks * TC5_KV_BYTES + blk * (TC5_KEYS * 128) + offset, &map_k, blk * 64, row, k_full + ks);
       }
       // values
-      if (lane == 0) {
-        if (i >= TC5_V_STAGES) ok = mbar_wait(v_empty + vs, ((i / TC5_V_STAGES) & 1) ^ 1, abort_flag);
-        if (ok) mbar_expect_tx(v_full + vs, TC5_KV_BYTES);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
+      if (lane == 0) mbar_expect_tx(v_full + vs, TC5_KV_BYTES);
       if (lane < pages_per_tile) {
 #pragma unroll
         for (int blk = 0; blk < D / 64; ++blk)
@@ -351,7 +350,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (active(0, 0)) issue_scores(0, 0);
         if (active(1, 0)) issue_scores(1, 0);
-        tc5_commit(k_empty);
+        tc5_commit(freed);
       }
       for (int i = 0; i < n_tiles && ok; ++i) {
         const int s = i % TC5_V_STAGES, next_k = (i + 1) % TC5_K_STAGES;
@@ -372,11 +371,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
             for (int kk = 1; kk < TC5_KEYS / 16; ++kk)
               tc5_mma_ts_acc(o_dst, p_src + kk * 8, vb + (uint64_t)(kk * (2048 >> 4)), idesc_pv);
-            tc5_commit(pv_done + x);
             ++done[x];
           }
-          // the value stage may be refilled when the products issued so far are done
-          if (x == 1) tc5_commit(v_empty + s);
           if (more && active(x, i + 1)) {
             // these scores overwrite P_x: the tensor core runs them after the product above
             if (!keys_ready) {
@@ -389,9 +385,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
         }
         if (!ok) break;
+        // event i + 1: value tile i and key tile i + 1 have been used by all that was issued
         if (more) {
-          if (!keys_ready) ok = mbar_wait(k_full + next_k, next_k_parity, abort_flag);
-          tc5_commit(k_empty + next_k);
+          if (!keys_ready) ok = mbar_wait(k_full + next_k, next_k_parity, abort_flag);   // keeps the phases in step
+          tc5_commit(freed + ((i + 1) & 3));
         }
       }
       tc5_commit(o_full);
@@ -476,11 +473,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       float sum0, sum1;
       tc5_unpair(tc5_add2(sum_a, sum_b), sum0, sum1);
       l = l * corr + (sum0 + sum1);
-      // O_x is only touched once the previous value product of this tile has finished;
-      // the next one is not issued before this warp has arrived below
+      // O_x is only touched once the previous value product of this tile has finished: the
+      // scores of this key tile were issued after it and the tensor core finishes in order, so
+      // it had when s_full completed.  The next one is not issued before this warp has arrived
+      // below.
       if (count > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-        if (!mbar_wait(pv_done + x, (count - 1) & 1, abort_flag)) { ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           float o[32];
