@@ -152,6 +152,8 @@ attn_decode_balanced_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
     for (int s = 0; s < TMA_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

@@ -571,6 +571,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
   *abort_flag = 1;
   return false;
 }
+// Asks for a tensor map ahead of the first copy that uses it.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -612,6 +616,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int my_tiles = max(0, tile_end - tile_begin);
 
   if (tid == 0) {
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
     for (int s = 0; s < TMA_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

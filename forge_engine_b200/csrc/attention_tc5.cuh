@@ -254,6 +254,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   };
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_q);
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
     mbar_init(q_full, 1);
     for (int s = 0; s < TC5_K_STAGES; ++s) mbar_init(k_full + s, 1);
     for (int s = 0; s < TC5_V_STAGES; ++s) mbar_init(v_full + s, 1);

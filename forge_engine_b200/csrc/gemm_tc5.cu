@@ -222,6 +222,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   const int my_blocks = max(0, kb_end - kb_begin);
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_w);
+    tma_prefetch_map(&map_x);
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
     mbar_init(acc_done, 1);
     *abort_flag = 0;

@@ -46,6 +46,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
   return false;
 }
 
+// Asks for a tensor map ahead of the first copy that uses it (the map is a kernel parameter;
+// the copy engine otherwise fetches its 128 bytes when that copy is issued).
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
