@@ -164,6 +164,9 @@ def test_steps_of_33_64_and_65_tokens(two_layers, dtype, monkeypatch) -> None:
     from forge_engine_b200.engine import StepEntry
     from forge_engine_b200.ops import native
 
+    # the launch counts below are those of the default settings
+    monkeypatch.delenv("FORGE_ENGINE_DECODE_CHAIN", raising=False)
+    monkeypatch.delenv("FORGE_ENGINE_SUMMED_QKV", raising=False)
     a, b = random_ids(5003, 33 + 40 + 65, 21), random_ids(5003, 24 + 9, 22)
     ref_a, ref_b = two_layers.plain_logits(a), two_layers.plain_logits(b)
     runner = two_layers.runner(dtype, pages=24, requests=2)
