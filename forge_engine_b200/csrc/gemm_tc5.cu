@@ -80,8 +80,14 @@ template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
   // blocks all run at once; the widest tile takes the SM alone.
   // (The gate/up product has about one block per SM; eight stages and the SM to itself for its
   // 64-token form measured worse, 6.44 against 5.81 ms per step at batch 64: the next product's
-  // blocks then find no room to become resident and fill their rings meanwhile.)
-  return BN <= 16 ? 6 : (BN <= 32 ? 5 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4)));
+  // blocks then find no room to become resident and fill their rings meanwhile.  Shallower
+  // rings with more blocks per SM for 16 tokens, -DFE_TC5_STAGES_16=5, 4, 3: 2.14, 2.20 and
+  // 2.36 ms per decode step at batch 1 against 2.11 ms with 6; 4 stages at batch 8: 2.52
+  // against 2.46 ms.)
+#ifndef FE_TC5_STAGES_16
+#define FE_TC5_STAGES_16 6
+#endif
+  return BN <= 16 ? FE_TC5_STAGES_16 : (BN <= 32 ? 5 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4)));
 }
 
 // Finished values of one accumulator row (feature) for 16 consecutive tokens.
@@ -511,7 +517,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 }
 
 template <int BN, int EPI> constexpr size_t smem_bytes() {
-  return (size_t)stages_for<BN, EPI>() * (BM * BK * 2 + BN * BK * 2) + (2 * stages_for<BN, EPI>() + 1) * 8 + 16 + 2 * 136 * 4 + 1024;
+  return (size_t)stages_for<BN, EPI>() * (BM * BK * 2 + BN * BK * 2) + (2 * stages_for<BN, EPI>() + 1) * 8 + 16 +
+         (EPI == EPI_QKV_ROPE ? 2 * 136 * 4 : 0) + 1024;
 }
 
 template <int BN, int EPI>
