@@ -359,8 +359,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int s = i % TC5_V_STAGES, next_k = (i + 1) % TC5_K_STAGES;
         const unsigned next_k_parity = ((i + 1) / TC5_K_STAGES) & 1;
         const bool more = i + 1 < n_tiles;
-        bool keys_ready = false;
+        // this tile's values and the next tile's keys: both were asked for long ago, and waiting
+        // for them here keeps the waits out of the stretch between a tile's P and its next scores
         ok = mbar_wait(v_full + s, (i / TC5_V_STAGES) & 1, abort_flag);
+        if (ok && more) ok = mbar_wait(k_full + next_k, next_k_parity, abort_flag);
 #pragma unroll
         for (int x = 0; x < 2 && ok; ++x) {
           if (active(x, i)) {
@@ -378,21 +380,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
           if (more && active(x, i + 1)) {
             // these scores overwrite P_x: the tensor core runs them after the product above
-            if (!keys_ready) {
-              ok = mbar_wait(k_full + next_k, next_k_parity, abort_flag);
-              if (!ok) break;
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-              keys_ready = true;
-            }
             issue_scores(x, i + 1);
           }
         }
         if (!ok) break;
         // event i + 1: value tile i and key tile i + 1 have been used by all that was issued
-        if (more) {
-          if (!keys_ready) ok = mbar_wait(k_full + next_k, next_k_parity, abort_flag);   // keeps the phases in step
-          tc5_commit(freed + ((i + 1) & 3));
-        }
+        if (more) tc5_commit(freed + ((i + 1) & 3));
       }
       tc5_commit(o_full);
     }
