@@ -129,14 +129,14 @@ class DecodeGraphs:
         return plan_batch(entries, self.cache, pad_counts=fillers, table_width=width,
                           null_page=self.cache.null_page, null_slot=self.cache.null_slot)
 
-    def _capture(self, key: tuple) -> _CapturedStep:
+    def _capture(self, key: tuple, counts: list) -> _CapturedStep:
+        """``counts``: tokens per entry of the step that asks for the capture, fillers included
+        (any split of the bucket's tokens over its entries has the same layout; this one is known
+        to fit block tables of the bucket's width)."""
         bucket_entries, bucket_tokens, width, plans = key
         device = self.model.ctx.device
         # A batch of filler entries only: it has the bucket's layout and is safe to run.
-        if bucket_tokens == bucket_entries:
-            fillers = [1] * bucket_entries
-        else:
-            fillers = [bucket_tokens - (bucket_entries - 1)] + [1] * (bucket_entries - 1)     # same layout, any split
+        fillers = list(counts)
         plan = self._plan([], fillers, width)
         assert plan.n_tokens == bucket_tokens and plan.n_entries == bucket_entries
         if bucket_tokens != bucket_entries:
@@ -188,7 +188,7 @@ class DecodeGraphs:
             self.seen[key] = sightings + 1
             if bucket_tokens != bucket_entries and sightings < self.capture_after:
                 return None
-            step = self._capture(key)
+            step = self._capture(key, [len(e.tokens) for e in entries] + fillers)
             self.captured[key] = step
         plan = self._plan(full, fillers, width)
         assert len(plan.flat) == step.buffer.numel()

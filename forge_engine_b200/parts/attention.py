@@ -231,14 +231,17 @@ class GQAttention(Mixer):
             # few tokens: the projection's k-splits add into a zeroed 32-bit buffer (no cluster,
             # more blocks), and the norm-and-rotate kernel reads the sums and leaves zeros behind
             width = self.qkv_proj.out_features
+            # everything the second kernel needs is at hand before the first is launched: the
+            # buffer is only zero again when both have run
+            angles = self.position.table(batch) if hasattr(self.position, "table") else None
+            qkv = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
             sums = native.projection_sums(x.device, x.shape[0] * width)[: x.shape[0] * width].view(x.shape[0], width)
             native.gemm_tc5(x, self.qkv_proj.weight, sums, native.TC5_ADD_F32, self.ctx.status, bias=self.qkv_proj.bias,
                             ksplit=native.tc5_ksplit_add(width, self.qkv_proj.in_features))
-            qkv = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
             native.qk_rope_cache_sums(
-                sums, qkv, self.q_norm, self.k_norm, self.spec.qk_norm_eps, None if rotary is None else rotary[0],
+                sums, qkv, self.q_norm, self.k_norm, self.spec.qk_norm_eps, rotary[0],
                 batch.positions, batch.token_entry, k_cache, v_cache, table, self.nq, cache.owns, self.ctx.status,
-                table=self.position.table(batch) if rotary is not None and hasattr(self.position, "table") else None,
+                table=angles,
             )
         elif self._fused_projection(x, rotary, k_cache):
             # few tokens, heads of 128: norm, rotation and the page write happen in the

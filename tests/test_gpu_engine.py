@@ -1004,6 +1004,28 @@ def test_mixed_steps_replayed_from_graphs_equal_eager_steps(fe, dtype, name, tmp
                 assert torch.equal(eager, replayed)
 
 
+def test_mixed_step_captured_with_narrow_block_tables(fe, tmp_path) -> None:
+    """A bucket's graph is captured with the token split of the step that asks for it: three
+    portions of 30 tokens with pages of 4 have block tables of 8 pages, and a capture that put
+    nearly all of the bucket's 96 tokens into one filler entry would need 24."""
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+
+    cfg, weights = make_model_folder(tmp_path / "m", plain.TINY_B, 2)
+    ids = {k: random_ids(cfg.vocab_size, 34, 300 + i) for i, k in enumerate("abc")}
+    runner = ModelRunner.from_folder(tmp_path / "m", dtype="float32", page_size=4, num_pages=64, max_requests=3)
+    runner.graphs.capture_after = 0
+    for k in ids:
+        runner.begin(k)
+    first = runner.step([StepEntry(k, ids[k][:30], [29]) for k in ids]).cpu()
+    assert any(key[:3] == (4, 96, 8) for key in runner.graphs.captured), list(runner.graphs.captured)
+    second = runner.step([StepEntry(k, ids[k][30:], [3]) for k in ids]).cpu()
+    runner.check_status()
+    for row, k in enumerate(ids):
+        ref = plain.forward_logits(ids[k], weights, cfg)
+        torch.testing.assert_close(first[row], ref[29], **bound("float32", ref))
+        torch.testing.assert_close(second[row], ref[33], **bound("float32", ref))
+
+
 def test_scheduler_run_with_buckets_captured_midway_gives_the_eager_tokens(fe, tmp_path) -> None:
     """A long scheduler run under a small token budget with the default capture policy: the
     buckets of its mixed steps are seen 16 times, captured in the middle of the run and
