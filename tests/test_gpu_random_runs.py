@@ -1,4 +1,7 @@
-"""Random scheduler runs: the same requests with steps replayed from CUDA graphs and launched
+"""Random runs: schedules and cuts drawn from seeds, where the hand-made traces of the other
+tests have fixed ones.
+
+Scheduler runs first: the same requests with steps replayed from CUDA graphs and launched
 eagerly must give the same tokens.
 
 Every trial draws a tiny configuration, a page size, a token budget, a portion size, a batch
@@ -65,3 +68,67 @@ def test_random_runs_with_and_without_graphs(seed, tmp_path) -> None:
         else:
             differing += sum(a != b for a, b in zip(outputs[True], outputs[False]))
     assert differing <= 4, f"{differing} bfloat16 requests differ between replayed and eager steps"
+
+
+@pytest.mark.parametrize("seed", [5, 23])
+def test_random_replays_at_the_benchmark_layer_sizes(seed) -> None:
+    """Random replays through ``ModelRunner.step`` at the benchmark model's layer sizes (two
+    layers; the tcgen05 products and attention kernels, the split and the balanced decode
+    kernels, the library product above 64 tokens) against the plain implementation: 3 to 8
+    requests of up to 1,200 tokens, up to 4 or 8 live, cut into single tokens, portions of 2
+    to 5 and portions of up to 900 tokens, requests left out of steps now and then, logits
+    wanted at random places, in 32-bit and bfloat16, replayed from graphs or launched eagerly."""
+    import torch
+
+    import test_gpu_real_sizes as sizes
+    from forge_engine_b200.engine import StepEntry
+
+    rng = random.Random(seed)
+    model = sizes.Model(sizes.TWO_LAYERS, 11)
+    for trial in range(6):
+        dtype = rng.choice(["float32", "bfloat16", "bfloat16"])
+        sequences = {f"r{i}": random_ids(5003, rng.randint(2, rng.choice([60, 300, 1200])), rng.randint(0, 10 ** 6))
+                     for i in range(rng.randint(3, 8))}
+        expected = {k: model.plain_logits(v) for k, v in sequences.items()}
+        live_max = rng.choice([4, 4, 8])
+        pages = sum(-(-len(v) // 16) for v in sequences.values()) + 1
+        runner = model.runner(dtype, pages=pages, requests=live_max, graphs=rng.random() < 0.7)
+        runner.graphs.capture_after = rng.choice([0, 2])
+        waiting = sorted(sequences)
+        rng.shuffle(waiting)
+        live, fed = [], {}
+        while waiting or live:
+            while waiting and len(live) < live_max and rng.random() < 0.7:
+                key = waiting.pop()
+                runner.begin(key)
+                live.append(key)
+                fed[key] = 0
+            entries = []
+            for key in live:
+                if rng.random() < 0.15 and len(live) > 1:
+                    continue
+                left = len(sequences[key]) - fed[key]
+                kind = rng.random()
+                count = 1 if kind < 0.45 else (rng.randint(2, 5) if kind < 0.65 else rng.randint(2, rng.choice([40, 70, 300, 900])))
+                count = max(1, min(count, left))
+                want = sorted(rng.sample(range(count), rng.randint(0, min(count, 3))))
+                entries.append(StepEntry(key, sequences[key][fed[key] : fed[key] + count], want))
+            if not entries:
+                continue
+            out = runner.step(entries).float().cpu()
+            row = 0
+            for entry in entries:
+                for j in entry.want:
+                    at = fed[entry.key] + j
+                    sizes.check_rows(dtype, out[row : row + 1], expected[entry.key][at : at + 1],
+                                     f"trial {trial}, {dtype}: {entry.key}[{at}] beside {[(e.key, len(e.tokens)) for e in entries]}")
+                    row += 1
+                fed[entry.key] += len(entry.tokens)
+            for key in [k for k in live if fed[k] == len(sequences[k])]:
+                runner.end(key)
+                live.remove(key)
+        runner.check_status()
+        runner.cache.check_consistency()
+        assert all(n == 0 for n in runner.cache.leased_pages())
+        del runner
+        torch.cuda.empty_cache()
