@@ -132,3 +132,45 @@ def test_random_replays_at_the_benchmark_layer_sizes(seed) -> None:
         assert all(n == 0 for n in runner.cache.leased_pages())
         del runner
         torch.cuda.empty_cache()
+
+
+def test_random_sampled_runs_with_end_tokens_and_tight_pools(tmp_path) -> None:
+    """Sampled requests (temperature, top-k, top-p, min-p, each with a seed of its own), an end
+    token in half of the models, and pools from just the largest request's pages upwards, so
+    that requests are put back and run again: with and without graphs, with and without
+    look-ahead, the four runs give the same tokens in 32-bit (a request's random stream is keyed
+    by its seed and its position, not by the step it is sampled in)."""
+    from forge_engine_b200.config import EngineConfig, SchedulerConfig
+    from forge_engine_b200.engine import Engine, ModelRunner
+    from forge_engine_b200.sampling import SamplingParams
+
+    rng = random.Random(29)
+    for trial in range(8):
+        name = rng.choice(sorted(CONFIGS))
+        raw, weight_seed = CONFIGS[name]
+        end = rng.choice([None, rng.randint(0, raw["vocab_size"] - 1)])
+        folder = tmp_path / f"{name}{trial}"
+        cfg, _ = make_model_folder(folder, dict(raw, eos_token_id=end), weight_seed)
+        page = rng.choice([4, 8, 16])
+        requests = rng.randint(5, 16)
+        prompts = [random_ids(cfg.vocab_size, rng.randint(1, 60), rng.randint(0, 10 ** 6)) for _ in range(requests)]
+        params = [SamplingParams(temperature=rng.choice([0.0, 0.0, 0.7, 1.0, 1.5]), top_k=rng.choice([None, 1, 5, 50]),
+                                 top_p=rng.choice([1.0, 0.9, 0.5]), min_p=rng.choice([0.0, 0.05]),
+                                 max_new_tokens=rng.randint(1, 14), seed=rng.randint(0, 10 ** 9)) for _ in range(requests)]
+        largest = max(-(-(len(p) + q.max_new_tokens) // page) + 1 for p, q in zip(prompts, params))
+        pages = largest + rng.choice([0, 2, 5, 20, 60])
+        outputs = {}
+        for graphs in (False, True):
+            for lookahead in (False, True):
+                scheduler = SchedulerConfig(max_requests=requests + 1, max_batch_size=4, token_budget=24, block_size=page,
+                                            block_capacity=pages, lookahead=lookahead)
+                runner = ModelRunner.from_folder(folder, dtype="float32", page_size=page, num_pages=pages,
+                                                 max_requests=requests + 1, use_graphs=graphs)
+                runner.graphs.capture_after = 1
+                engine = Engine(runner, EngineConfig(dtype="float32"), scheduler)
+                outputs[(graphs, lookahead)] = engine.generate(prompts, params)
+                runner.cache.check_consistency()
+                assert all(n == 0 for n in runner.cache.leased_pages())
+        first = outputs[(False, False)]
+        differ = [key for key, tokens in outputs.items() if tokens != first]
+        assert not differ, f"trial {trial}: {name}, pages of {page}, pool {pages} (largest request {largest}), end token {end}: {differ}"
