@@ -174,3 +174,60 @@ def test_random_sampled_runs_with_end_tokens_and_tight_pools(tmp_path) -> None:
         first = outputs[(False, False)]
         differ = [key for key, tokens in outputs.items() if tokens != first]
         assert not differ, f"trial {trial}: {name}, pages of {page}, pool {pages} (largest request {largest}), end token {end}: {differ}"
+
+
+def test_random_configurations_of_the_architecture(tmp_path) -> None:
+    """Configurations drawn from a seed - head sizes in steps of 16 up to 256, 1 to 4 key/value
+    heads with 1 to 8 query heads each, widths and feed-forward widths in steps of 8, 1 to 4
+    layers, any vocabulary from 20 to 700, windows on none, some or all layers, tied or untied
+    embeddings, with and without projection bias, several eps and theta - each built from a
+    model folder and stepped in 32-bit and in bfloat16 with three requests cut at random,
+    against the plain implementation."""
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+
+    rng = random.Random(53)
+    for trial in range(8):
+        d = 16 * rng.randint(1, 8) if rng.random() < 0.7 else rng.choice([64, 128, 256])
+        nkv, groups, layers = rng.choice([1, 2, 3, 4]), rng.choice([1, 2, 3, 4, 6, 8]), rng.randint(1, 4)
+        window = rng.choice([None, None, 5, 11, 33, 70, 130])
+        raw = dict(plain.TINY_A, vocab_size=rng.randint(20, 700), hidden_size=8 * rng.randint(2, 40),
+                   intermediate_size=8 * rng.randint(2, 60), num_hidden_layers=layers, num_attention_heads=nkv * groups,
+                   num_key_value_heads=nkv, head_dim=d, rms_norm_eps=rng.choice([1e-6, 1e-5, 3e-4]),
+                   rope_theta=rng.choice([1e4, 5e5, 1e6, 1234.5]), tie_word_embeddings=rng.random() < 0.5,
+                   attention_bias=rng.random() < 0.3, eos_token_id=None)
+        if window is not None:
+            raw.update(use_sliding_window=True, sliding_window=window, max_window_layers=rng.randint(0, layers))
+        described = {k: raw[k] for k in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                         "num_attention_heads", "num_key_value_heads", "head_dim", "sliding_window")}
+        cfg, weights = make_model_folder(tmp_path / f"m{trial}", raw, trial)
+        sequences = {f"r{i}": random_ids(cfg.vocab_size, rng.randint(2, 220), rng.randint(0, 10 ** 6)) for i in range(3)}
+        expected = {k: plain.forward_logits(v, weights, cfg) for k, v in sequences.items()}
+        for dtype in ("float32", "bfloat16"):
+            page = rng.choice([4, 8, 16, 32])
+            pages = sum(-(-len(v) // page) for v in sequences.values()) + 2
+            runner = ModelRunner.from_folder(tmp_path / f"m{trial}", dtype=dtype, page_size=page, num_pages=pages,
+                                             max_requests=3, use_graphs=rng.random() < 0.6)
+            runner.graphs.capture_after = 0
+            fed = {k: 0 for k in sequences}
+            for key in sequences:
+                runner.begin(key)
+            while any(fed[k] < len(sequences[k]) for k in sequences):
+                entries = []
+                for key in sequences:
+                    left = len(sequences[key]) - fed[key]
+                    if left:
+                        count = min(left, rng.choice([1, 1, 2, 3, 17, 64, 100, 200]))
+                        entries.append(StepEntry(key, sequences[key][fed[key] : fed[key] + count], sorted({0, count - 1})))
+                out = runner.step(entries).float().cpu()
+                row = 0
+                for entry in entries:
+                    for j in entry.want:
+                        ref = expected[entry.key][fed[entry.key] + j]
+                        limit = 3e-5 if dtype == "float32" else 3e-2 * max(1.0, float(ref.abs().max()))
+                        error = float((out[row] - ref).abs().max())
+                        assert error <= limit, f"trial {trial} {described}, {dtype}, pages of {page}: {entry.key}[{fed[entry.key] + j}] {error:.3e}"
+                        row += 1
+                    fed[entry.key] += len(entry.tokens)
+            for key in sequences:
+                runner.end(key)
+            runner.check_status()
