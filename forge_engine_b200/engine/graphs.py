@@ -19,8 +19,8 @@ step is captured once per *bucket* and replayed:
   not depend on which entries do.
 
 A decode step is captured the first time its bucket is seen.  A bucket of any other step is
-captured only when it has been seen ``capture_after`` times (16): a capture takes two eager
-passes and the capture itself, about 0.1 s at 36 layers, and a replay saves a millisecond
+captured only when it has been seen ``capture_after`` times (16): a capture takes an eager
+pass and the capture itself, up to 0.1 s at 36 layers, and a replay saves a millisecond
 or two, so shapes that rarely come back are not worth it (64 requests of 16 to 4,096 tokens
 under a budget of 2,048 at the 8B shape: 3.97 s without such captures, 4.4 to 7.2 s when every
 bucket seen twice was captured).  Replay would gain even for a 2,048-token prompt (15.3
@@ -147,8 +147,9 @@ class DecodeGraphs:
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):
-            for _ in range(2):  # lazy initialisation (handles, attributes) must not be captured
-                self.model.forward(batch, self.cache)
+            # lazy initialisation (handles, function attributes, scratch buffers of this size) must
+            # not be captured: one eager pass over the same batch does all of it
+            self.model.forward(batch, self.cache)
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         graph = torch.cuda.CUDAGraph()
