@@ -83,7 +83,8 @@ template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
   // blocks then find no room to become resident and fill their rings meanwhile.  Shallower
   // rings with more blocks per SM for 16 tokens, -DFE_TC5_STAGES_16=5, 4, 3: 2.14, 2.20 and
   // 2.36 ms per decode step at batch 1 against 2.11 ms with 6; 4 stages at batch 8: 2.52
-  // against 2.46 ms.)
+  // against 2.46 ms.  The gate/up product alone with 5, 8 or 12 stages at batch 8: 2.47, 2.94
+  // and 2.96 ms: from 7 stages on no second block fits on the SM.)
 #ifndef FE_TC5_STAGES_16
 #define FE_TC5_STAGES_16 6
 #endif
