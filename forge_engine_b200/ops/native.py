@@ -548,7 +548,20 @@ def tc5_ksplit_add(o: int, k: int) -> int:
     2.51 with 14 or 15, 2.72 with 16 - 320 blocks no longer run in one round).  A block keeps
     at least four 64-wide k-blocks."""
     tiles = -(-o // 128)
-    return max(1, min(_ADD_LIMIT, round(_ADD_TARGET / tiles), (k // 64) // 4))
+    fits = max(1, _resident_blocks() // tiles)          # never more blocks than run at once
+    return max(1, min(_ADD_LIMIT, round(_ADD_TARGET / tiles), fits, (k // 64) // 4))
+
+
+_RESIDENT_BLOCKS = 0
+
+
+def _resident_blocks() -> int:
+    """Blocks of the tcgen05 product for few tokens that the GPU holds at once: two per SM."""
+    global _RESIDENT_BLOCKS
+    if not _RESIDENT_BLOCKS:
+        _RESIDENT_BLOCKS = int(_os.environ.get("FORGE_ENGINE_RESIDENT_BLOCKS", "0")) or \
+            2 * torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _RESIDENT_BLOCKS
 
 
 def tc5_ksplit(o: int, k: int) -> int:
