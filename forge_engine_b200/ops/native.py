@@ -545,8 +545,10 @@ def tc5_ksplit_add(o: int, k: int) -> int:
     partial sums meet in memory through atomic adds, so the k-splits need not form a cluster
     and there may be more of them: about 288 blocks, just under the 296 a B200 holds at once
     (measured at the 4B shape, batch 8, per decode step: 2.60 ms with 8 splits, 2.53 with 12,
-    2.51 with 14 or 15, 2.72 with 16 - 320 blocks no longer run in one round).  A block keeps
-    at least four 64-wide k-blocks."""
+    2.51 with 14 or 15, 2.72 with 16 - 320 blocks no longer run in one round).  So whatever the
+    number of tiles, the splits never make more blocks than are resident at once (two per SM;
+    FORGE_ENGINE_RESIDENT_BLOCKS overrides the count).  A block keeps at least four 64-wide
+    k-blocks."""
     tiles = -(-o // 128)
     fits = max(1, _resident_blocks() // tiles)          # never more blocks than run at once
     return max(1, min(_ADD_LIMIT, round(_ADD_TARGET / tiles), fits, (k // 64) // 4))
