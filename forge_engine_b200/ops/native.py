@@ -554,6 +554,22 @@ def tc5_ksplit_add(o: int, k: int) -> int:
     return max(1, min(_ADD_LIMIT, round(_ADD_TARGET / tiles), fits, (k // 64) // 4))
 
 
+_SUMS_TARGET = int(_os.environ.get("FORGE_ENGINE_SUMS_BLOCKS", "0"))
+
+
+def tc5_ksplit_sums(o: int, k: int, n: int) -> int:
+    """Blocks per 128-feature tile of the q/k/v projection that adds its k-splits into 32-bit
+    sums for ``n`` tokens.  Up to 16 tokens it aims at 240 blocks instead of 288: the attention
+    kernel that follows finds room on more SMs while the projection still runs and has keys in
+    flight earlier (4B shape, 48 tiles, per decode step at batch 1 / 8 / 16: 2.098 / 2.445 /
+    2.915 ms with 5 splits against 2.105 / 2.460 / 2.929 with 6; at batch 32 and 64 six are
+    better, 3.819 / 5.775 against 3.840 / 5.796 ms).  FORGE_ENGINE_SUMS_BLOCKS names another
+    number of blocks to aim at."""
+    target = _SUMS_TARGET or (240 if n <= 16 else _ADD_TARGET)
+    tiles = -(-o // 128)
+    return max(1, min(_ADD_LIMIT, round(target / tiles), max(1, _resident_blocks() // tiles), (k // 64) // 4))
+
+
 _RESIDENT_BLOCKS = 0
 
 

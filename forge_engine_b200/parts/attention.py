@@ -237,7 +237,7 @@ class GQAttention(Mixer):
             qkv = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
             sums = native.projection_sums(x.device, x.shape[0] * width)[: x.shape[0] * width].view(x.shape[0], width)
             native.gemm_tc5(x, self.qkv_proj.weight, sums, native.TC5_ADD_F32, self.ctx.status, bias=self.qkv_proj.bias,
-                            ksplit=native.tc5_ksplit_add(width, self.qkv_proj.in_features))
+                            ksplit=native.tc5_ksplit_sums(width, self.qkv_proj.in_features, x.shape[0]))
             native.qk_rope_cache_sums(
                 sums, qkv, self.q_norm, self.k_norm, self.spec.qk_norm_eps, rotary[0],
                 batch.positions, batch.token_entry, k_cache, v_cache, table, self.nq, cache.owns, self.ctx.status,
