@@ -548,6 +548,9 @@ def main() -> int:
     parser.add_argument("--step-timeline", action="store_true",
                         help="also print, per kernel of one replayed decode step, the time from the end of the kernel "
                              "before it to its own end (for profiles/)")
+    parser.add_argument("--mixed-only", type=int, metavar="TOKENS",
+                        help="only the mixed step: 8 requests decoding beside a prompt portion, TOKENS tokens in all "
+                             "(with --kernel-times: the kernels of one such step)")
     parser.add_argument("--kernel-times", action="store_true",
                         help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()
@@ -751,6 +754,31 @@ def main() -> int:
                 runner.end("kt")
 
             kernel_times(one_prefill)
+        print(json.dumps(record))
+        return 0
+
+    if args.mixed_only:
+        tokens, decoders = args.mixed_only, 8
+        mixed = mixed_run(tokens, decoders, max(1, args.steps if args.steps != 200 else 20), 24)
+        record = {"mixed": {"tokens": tokens, "decoding": decoders, "ms_wall": round(mixed["ms_wall"], 3),
+                            "ms_device": round(mixed["ms_device"], 3),
+                            "value": round(tokens / (mixed["ms_device"] / 1e3), 1)}, "layers": layers, "impl": "ours"}
+        if args.kernel_times:
+            keys = [f"mk{i}" for i in range(decoders)]
+            for key in keys:
+                runner.begin(key)
+                runner.cache.reserve(key, CONTEXT)
+                runner.cache.advance(key, CONTEXT)
+            portion = torch.randint(0, raw["vocab_size"], (tokens - decoders,), generator=gen).tolist()
+
+            def one_mixed():
+                runner.begin("mkp")
+                runner.step([StepEntry(k, [7], [0]) for k in keys] + [StepEntry("mkp", portion, [])])
+                runner.end("mkp")
+
+            for _ in range(20):        # let the step's bucket be captured: the table is of a replayed step
+                one_mixed()
+            kernel_times(one_mixed)
         print(json.dumps(record))
         return 0
 
